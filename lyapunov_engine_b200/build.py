@@ -46,7 +46,8 @@ HOST_SOURCES = ["host/block_manager.cpp", "host/scheduler.cpp", "host/step_pack.
 CORE_KERNEL_SOURCES = ["kernels/elementwise.cu", "kernels/norm.cu", "kernels/rope_kv.cu",
                        "kernels/gemm_f32.cu", "kernels/sampling.cu", "kernels/gemm_skinny.cu", "kernels/gemm_tc.cu",
                        "kernels/short_conv.cu", "kernels/kv_store.cu", "kernels/gemm_heads.cu", "kernels/streams.cu",
-                       "kernels/rope_pairs.cu", "kernels/moe.cu"]
+                       "kernels/rope_pairs.cu", "kernels/moe.cu", "kernels/delta_rule.cu", "kernels/rope_norm.cu",
+                       "kernels/residual.cu"]
 ATTENTION_SOURCES = ["kernels/attention_generic.cu", "kernels/attention_mma.cu", "kernels/attention_tc.cu"]
 
 _lock = threading.Lock()

@@ -56,15 +56,18 @@ __global__ void embed_sinusoid_kernel(float *__restrict__ out, const T *__restri
   }
 }
 
-// out[t, i] = act(gu[t, i], gu[t, I + i]) (le::gated_activation), in 32-bit, rounded once.
+// out[t, i] = act(gu[t, i] + bias[i], gu[t, I + i] + bias[I + i]) (le::gated_activation; bias null: none), in 32-bit,
+// rounded once.
 template <typename T>
-__global__ void glu_kernel(T *__restrict__ out, const T *__restrict__ gu, int64_t total, int inter, le::GatedActivation act) {
+__global__ void glu_kernel(T *__restrict__ out, const T *__restrict__ gu, int64_t total, int inter, le::GatedActivation act,
+                           const float *__restrict__ bias) {
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const int64_t t = idx / inter;
   const int i = static_cast<int>(idx - t * inter);
-  const float g = le::to_f32(gu[t * 2 * inter + i]);
-  const float u = le::to_f32(gu[t * 2 * inter + inter + i]);
+  float g = le::to_f32(gu[t * 2 * inter + i]);
+  float u = le::to_f32(gu[t * 2 * inter + inter + i]);
+  if (bias != nullptr) g += bias[i], u += bias[inter + i];
   out[idx] = le::from_f32<T>(le::gated_activation(g, u, act));
 }
 
@@ -213,8 +216,16 @@ LE_API int le_embed_sinusoid(float *out, const void *table, int table_dtype, con
 }
 
 // out[T, I] from gate_up[T, 2 I] (gate columns first) by the activation `kind` (see le::GatedActivation).
+LE_API int le_glu_bias(void *out, const void *gate_up, int dtype, int num_tokens, int inter, int kind, float alpha,
+                       float limit, const float *bias, cudaStream_t stream);
 LE_API int le_glu(void *out, const void *gate_up, int dtype, int num_tokens, int inter, int kind, float alpha, float limit,
                   cudaStream_t stream) {
+  return le_glu_bias(out, gate_up, dtype, num_tokens, inter, kind, alpha, limit, nullptr, stream);
+}
+
+// The same with a bias [2 I] (float32; gate's entries first) added to the product's columns before the activation.
+LE_API int le_glu_bias(void *out, const void *gate_up, int dtype, int num_tokens, int inter, int kind, float alpha,
+                       float limit, const float *bias, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (kind < 0 || kind > 2) return le::invalid("le_glu: unknown activation %d", kind);
   const int64_t total = static_cast<int64_t>(num_tokens) * inter;
@@ -223,7 +234,7 @@ LE_API int le_glu(void *out, const void *gate_up, int dtype, int num_tokens, int
   if (blocks > 2147483647LL) return le::invalid("le_glu: %lld elements are too many for one launch", (long long)total);
   LE_DISPATCH_DTYPE(dtype, T,
                     glu_kernel<T><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
-                        static_cast<T *>(out), static_cast<const T *>(gate_up), total, inter, le::GatedActivation{kind, alpha, limit}));
+                        static_cast<T *>(out), static_cast<const T *>(gate_up), total, inter, le::GatedActivation{kind, alpha, limit}, bias));
   return le::launched();
 }
 

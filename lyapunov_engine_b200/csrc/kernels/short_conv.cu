@@ -72,7 +72,8 @@ template <typename T, int VEC>
 __global__ void __launch_bounds__(CONV_THREADS)
 short_conv_kernel(T *__restrict__ out, const T *__restrict__ h, const float *__restrict__ w, float *__restrict__ state,
                   int num_state_rows, const int32_t *__restrict__ state_slots, const int32_t *__restrict__ cu_q,
-                  const int32_t *__restrict__ tile_request, const int32_t *__restrict__ tile_q0, int channels, int taps) {
+                  const int32_t *__restrict__ tile_request, const int32_t *__restrict__ tile_q0, int channels, int taps,
+                  int64_t h_stride, int add_input, int activation) {
   le::let_successor_start();
   const int r = threadIdx.x / CONV_LANES;                                   // this thread's token within the tile
   const int c = (blockIdx.y * CONV_LANES + threadIdx.x % CONV_LANES) * VEC;  // its first channel
@@ -103,16 +104,21 @@ short_conv_kernel(T *__restrict__ out, const T *__restrict__ h, const float *__r
   if (writes_state && new_src < 0) load_channels<float, VEC>(carry, mine + static_cast<int64_t>(keep + new_src) * channels);
 
   le::wait_for_predecessor();
-  const T *hx = h + static_cast<int64_t>(first) * channels + c;
+  const T *hx = h + static_cast<int64_t>(first) * h_stride + c;
   if (live) {
     float acc[VEC];
-    load_channels<T, VEC>(acc, hx + static_cast<int64_t>(q) * channels);
+    if (add_input) {
+      load_channels<T, VEC>(acc, hx + static_cast<int64_t>(q) * h_stride);
+    } else {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc[e] = 0.0f;
+    }
     for (int j = 0; j < taps; ++j) {
       const int src = q - (keep - j);
       float v[VEC], wt[VEC];
       load_channels<float, VEC>(wt, w + static_cast<int64_t>(j) * channels + c);
       if (src >= 0) {
-        load_channels<T, VEC>(v, hx + static_cast<int64_t>(src) * channels);
+        load_channels<T, VEC>(v, hx + static_cast<int64_t>(src) * h_stride);
       } else if (mine) {          // (src < 0 only in the request's first tile)
         load_channels<float, VEC>(v, mine + static_cast<int64_t>(keep + src) * channels);
       } else {
@@ -122,16 +128,28 @@ short_conv_kernel(T *__restrict__ out, const T *__restrict__ h, const float *__r
 #pragma unroll
       for (int e = 0; e < VEC; ++e) acc[e] = fmaf(wt[e], v[e], acc[e]);
     }
+    if (activation == 1) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc[e] = acc[e] / (1.0f + expf(-acc[e]));
+    }
     store_channels<T, VEC>(out + (static_cast<int64_t>(first) + q) * channels + c, acc);
   }
   __syncthreads();       // every read of the old state is done
   if (writes_state) {
-    if (new_src >= 0) load_channels<T, VEC>(carry, hx + static_cast<int64_t>(new_src) * channels);
+    if (new_src >= 0) load_channels<T, VEC>(carry, hx + static_cast<int64_t>(new_src) * h_stride);
     store_channels<float, VEC>(mine + static_cast<int64_t>(r) * channels, carry);
   }
 }
 
 }  // namespace
+
+// The general form: rows of h are h_stride elements apart (the channels are the first `channels` columns of wider
+// rows); add_input 0 leaves the token's own input out of the sum (a plain convolution, whose last tap is the current
+// token's); activation 1 puts silu over the sum.
+LE_API int le_short_conv_general(void *out, const void *h, int64_t h_stride, int dtype, const float *w, float *state,
+                                 int num_state_rows, const int32_t *state_slots, const int32_t *cu_q,
+                                 const int32_t *tile_request, const int32_t *tile_q0, int num_tiles, int tile, int channels,
+                                 int taps, int add_input, int activation, cudaStream_t stream);
 
 // out, h: [tokens, channels] contiguous (different buffers); w: [taps, channels] float32; state:
 // [num_state_rows, taps - 1, channels] float32 (may be null when taps is 1); the tiles list `tile` tokens each.
@@ -139,14 +157,23 @@ short_conv_kernel(T *__restrict__ out, const T *__restrict__ h, const float *__r
 LE_API int le_short_conv(void *out, const void *h, int dtype, const float *w, float *state, int num_state_rows,
                          const int32_t *state_slots, const int32_t *cu_q, const int32_t *tile_request,
                          const int32_t *tile_q0, int num_tiles, int tile, int channels, int taps, cudaStream_t stream) {
+  return le_short_conv_general(out, h, channels, dtype, w, state, num_state_rows, state_slots, cu_q, tile_request, tile_q0,
+                               num_tiles, tile, channels, taps, 1, 0, stream);
+}
+
+LE_API int le_short_conv_general(void *out, const void *h, int64_t h_stride, int dtype, const float *w, float *state,
+                                 int num_state_rows, const int32_t *state_slots, const int32_t *cu_q,
+                                 const int32_t *tile_request, const int32_t *tile_q0, int num_tiles, int tile, int channels,
+                                 int taps, int add_input, int activation, cudaStream_t stream) {
   if (num_tiles <= 0 || channels <= 0) return 0;
+  if (h_stride < channels) return le::invalid("le_short_conv: rows of %lld elements hold no %d channels", (long long)h_stride, channels);
   if (taps < 1 || taps > CONV_MAX_TAPS) return le::invalid("le_short_conv: taps must be 1..%d, got %d", CONV_MAX_TAPS, taps);
   if (tile != CONV_TILE) return le::invalid("le_short_conv: the tiles must list %d tokens each, not %d", CONV_TILE, tile);
   if (out == h) return le::invalid("le_short_conv: out and h must be different buffers");
   if ((tile_request == nullptr) != (tile_q0 == nullptr)) return le::invalid("le_short_conv: both tile lists or neither");
   const int vec = dtype == LE_BF16 ? 8 : 4;
   // 16-byte accesses to the rows (vec values of the type) and to weights and state (two or one of them per access)
-  const bool wide = channels % 8 == 0 &&
+  const bool wide = channels % 8 == 0 && h_stride % 8 == 0 &&
                     ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(w) |
                       reinterpret_cast<uintptr_t>(state)) & 15) == 0;
   const int per_block = CONV_LANES * (wide ? vec : 1);
@@ -155,7 +182,7 @@ LE_API int le_short_conv(void *out, const void *h, int dtype, const float *w, fl
 #define LE_GO(T, V)                                                                                                  \
   return le::launch_chained(short_conv_kernel<T, V>, grid, dim3(CONV_THREADS), 0, stream, static_cast<T *>(out),     \
                             static_cast<const T *>(h), w, state, num_state_rows, state_slots, cu_q, tile_request,    \
-                            tile_q0, channels, taps)
+                            tile_q0, channels, taps, h_stride, add_input, activation)
   if (dtype == LE_BF16) { if (wide) LE_GO(__nv_bfloat16, 8); LE_GO(__nv_bfloat16, 1); }
   if (dtype == LE_F32) { if (wide) LE_GO(float, 4); LE_GO(float, 1); }
 #undef LE_GO

@@ -10,7 +10,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 
 from .. import ops
-from ..parts.base import (BLOCKS, EMBEDDINGS, HEADS, NORMS, KVNeed, ModelSpec, ResidualStream, StateNeed,
+from ..parts.base import (BLOCKS, EMBEDDINGS, HEADS, NORMS, STREAM_INPUTS, KVNeed, ModelSpec, ResidualStream, StateNeed,
                           TensorDecl)
 
 
@@ -40,6 +40,8 @@ class Model:
         self.spec = spec
         self.embedding = EMBEDDINGS.build(spec.embedding)
         self.blocks = [BLOCKS.build(layer.block) for layer in spec.layers]
+        # what runs right before a run's layer (None: nothing)
+        self.entries = [STREAM_INPUTS.build(run.entry) if run.entry is not None else None for run in spec.run_order]
         self.final_norm = NORMS.build(spec.final_norm)
         self.head = HEADS.build(spec.head)
         self.groups: list[CacheGroupPlan] = []
@@ -93,7 +95,7 @@ class Model:
 
     # ---- tensors
     def parts(self):
-        return [self.embedding, *self.blocks, self.final_norm, self.head]
+        return [self.embedding, *self.blocks, *(e for e in self.entries if e is not None), self.final_norm, self.head]
 
     def tensors(self) -> list[TensorDecl]:
         seen: dict[str, TensorDecl] = {}
@@ -137,6 +139,8 @@ class Model:
         resid = self.embedding.forward(ctx)
         stream = ResidualStream(resid)
         for index, run in enumerate(self.runs):
+            if self.entries[index] is not None:
+                self.entries[index].forward(stream, ctx)
             self.blocks[run.layer].forward(stream, ctx, cache.binding(index))
             if observe is not None:
                 observe(index, stream)

@@ -80,6 +80,28 @@ _CORE_SIGNATURES = {
     "le_head_gate": [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p],
     "le_short_conv": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                       c_int, c_int, c_int, c_void_p],
+    "le_short_conv_general": [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "le_glu_bias": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p],
+    "le_gated_delta_lanes": [c_int],
+    "le_gated_delta_scan": [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_int64, c_int, c_int, c_int,
+                            c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                            c_float, c_float, c_void_p],
+    "le_head_norm_gate": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p, c_float, c_int, c_int,
+                          c_int, c_void_p],
+    "le_rope_norm_store": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_int,
+                           c_void_p, c_void_p],
+    "le_latent_rope_store": [c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p,
+                             c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                             c_int, c_void_p, c_void_p],
+    "le_rmsnorm_pair": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_float, c_void_p,
+                        c_void_p, c_float, c_void_p, c_int, c_int, c_void_p],
+    "le_residual_add": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int64, c_void_p, c_int, c_int, c_int64,
+                        c_void_p, c_int, c_int, c_void_p],
+    "le_gate_rows": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64, c_int, c_void_p, c_int, c_int, c_int, c_void_p,
+                     c_void_p],
+    "le_stream_entry": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "le_kv_store": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                     c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "le_latent_norm_store": [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p,
@@ -283,15 +305,18 @@ def swiglu(out: torch.Tensor, gate_up: torch.Tensor) -> None:
 GLU_SILU, GLU_CLAMPED, GLU_RELU = 0, 1, 2
 
 
-def glu(out: torch.Tensor, gate_up: torch.Tensor, kind: int = GLU_SILU, alpha: float = 1.0, limit: float = 0.0) -> None:
-    """out[t, i] from gate g = gate_up[t, i] and u = gate_up[t, I + i].
+def glu(out: torch.Tensor, gate_up: torch.Tensor, kind: int = GLU_SILU, alpha: float = 1.0, limit: float = 0.0,
+        bias=None) -> None:
+    """out[t, i] from gate g = gate_up[t, i] and u = gate_up[t, I + i], each
+    plus its entry of ``bias`` (float32 [2 I]) where one is given.
     GLU_SILU: silu(g) * u.  GLU_CLAMPED: g' = min(g, limit), u' = clamp(u,
     -limit, limit); g' * sigmoid(alpha * g') * (u' + 1).  GLU_RELU: max(g, 0) * u."""
-    _need_cuda(out, gate_up)
+    _need_cuda(out, gate_up, bias)
     T, I = out.shape
     assert gate_up.shape == (T, 2 * I) and out.is_contiguous() and gate_up.is_contiguous() and out.dtype == gate_up.dtype
-    _check(core().le_glu(_ptr(out), _ptr(gate_up), dtype_code(out.dtype), T, I, int(kind), float(alpha), float(limit),
-                         _stream()), "le_glu")
+    assert bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == 2 * I)
+    _check(core().le_glu_bias(_ptr(out), _ptr(gate_up), dtype_code(out.dtype), T, I, int(kind), float(alpha), float(limit),
+                              _ptr(bias), _stream()), "le_glu_bias")
 
 
 def embed_sinusoid(out_resid, table, ids, positions, rates, status) -> None:
@@ -688,6 +713,17 @@ def gated_linear(out: torch.Tensor, a: torch.Tensor, w_gate_up: torch.Tensor, wo
     gu = workspace.get("gate_up", (a.shape[0], w_gate_up.shape[0]), a.dtype)
     linear(gu, a, w_gate_up, status)
     glu(out, gu, *activation)
+
+
+def gated_linear_bias(out: torch.Tensor, a: torch.Tensor, w_gate_up: torch.Tensor, bias: torch.Tensor, workspace, status=None,
+                      activation=(GLU_SILU, 1.0, 0.0)) -> None:
+    """gated_linear() with a bias [2 I] (float32) on the product's columns
+    before the activation: the product, then the activation's kernel with the
+    bias (the sums, the bias and the activation in 32 bits where the product
+    writes 32-bit columns: few rows)."""
+    gu = workspace.get("gate_up", (a.shape[0], w_gate_up.shape[0]), a.dtype)
+    linear(gu, a, w_gate_up, status)
+    glu(out, gu, *activation, bias=bias)
 
 
 def linear(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, status=None) -> None:
@@ -1132,3 +1168,189 @@ def moe_combine(out, y, top: int, shared_out=None, gate=None) -> None:
     assert shared_out is None or (shared_out.dtype == out.dtype and shared_out.is_contiguous() and shared_out.shape == out.shape)
     _check(core().le_moe_combine(_ptr(out), dtype_code(out.dtype), _ptr(y), _ptr(shared_out), _ptr(gate), T, W, top, _stream()),
            "le_moe_combine")
+
+
+# -------------------------------------------------------------------------- convolution with activation, delta rule
+def short_conv_general(out, h, w_taps, state, state_slots, cu_q, tile_request, tile_q0, num_tiles, add_input: bool,
+                       silu: bool) -> None:
+    """short_conv() in its general form: ``h`` may be the first columns of
+    wider rows (any row stride); ``add_input`` False leaves the token's own
+    input out of the sum (a plain causal convolution whose last tap is the
+    current token's); ``silu`` puts silu over the sum."""
+    _need_cuda(out, h, w_taps, state, state_slots, cu_q)
+    T, C = h.shape
+    taps = w_taps.shape[0]
+    assert out.shape == h.shape and out.dtype == h.dtype and out.is_contiguous() and h.stride(1) == 1
+    assert w_taps.dtype == torch.float32 and w_taps.is_contiguous() and w_taps.shape[1] == C
+    rows = 0
+    if taps > 1:
+        assert state is not None and state.dtype == torch.float32 and state.is_contiguous()
+        assert tuple(state.shape[1:]) == (taps - 1, C)
+        rows = state.shape[0]
+    _check(core().le_short_conv_general(_ptr(out), _ptr(h), h.stride(0), dtype_code(h.dtype), _ptr(w_taps),
+                                        _ptr(state) if taps > 1 else None, rows, _ptr(state_slots), _ptr(cu_q),
+                                        _ptr(tile_request), _ptr(tile_q0), num_tiles, SHORT_CONV_TILE, C, taps,
+                                        1 if add_input else 0, 1 if silu else 0, _stream()), "le_short_conv_general")
+
+
+GATED_DELTA_MAX_DIM = 1024
+
+
+def gated_delta_scan(out, qkv, q_col, k_col, v_col, proj, b_col, a_col, a_log, dt_bias, state, state_slots, cu_q,
+                     num_requests, heads, kv_heads, dim, vdim, unit_eps, q_scale) -> None:
+    """The gated delta rule over the step's tokens, request by request, from
+    each request's state row and back into it.  ``out``: float32 [T, heads *
+    vdim].  ``qkv``: rows with queries and keys [kv_heads, dim] at columns
+    ``q_col`` / ``k_col`` and values [heads, vdim] at ``v_col``; queries and
+    keys are made unit vectors here (x / sqrt(sum x^2 + unit_eps)), queries
+    times ``q_scale``.  ``proj``: rows with one number per head at ``b_col``
+    (step size = its sigmoid) and ``a_col`` (decay = exp(-exp(a_log) *
+    softplus(a + dt_bias))).  ``state``: float32 [rows, heads, vdim, dim]."""
+    _need_cuda(out, qkv, proj, a_log, dt_bias, state, state_slots, cu_q)
+    assert out.dtype == torch.float32 and out.stride(1) == 1 and qkv.stride(1) == 1 and proj.stride(1) == 1
+    assert qkv.dtype == proj.dtype and a_log.dtype == torch.float32 and dt_bias.dtype == torch.float32
+    assert a_log.numel() == heads and dt_bias.numel() == heads
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, vdim, dim)
+    _check(core().le_gated_delta_scan(_ptr(out), out.stride(0), _ptr(qkv), qkv.stride(0), q_col, k_col, v_col, _ptr(proj),
+                                      proj.stride(0), b_col, a_col, dtype_code(qkv.dtype), _ptr(a_log), _ptr(dt_bias),
+                                      _ptr(state), state.shape[0], _ptr(state_slots), _ptr(cu_q), num_requests, heads,
+                                      kv_heads, dim, vdim, float(unit_eps), float(q_scale), _stream()),
+           "le_gated_delta_scan")
+
+
+def head_norm_gate(out, o, gate, weight, eps, heads, vdim) -> None:
+    """out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight *
+    silu(gate[t, h, :]); ``o`` float32, ``gate`` and ``out`` in the
+    activations' type (column ranges of wider rows are fine)."""
+    _need_cuda(out, o, gate, weight)
+    T = o.shape[0]
+    assert o.dtype == torch.float32 and o.shape == (T, heads * vdim) and out.shape == o.shape and gate.shape == o.shape
+    assert out.dtype == gate.dtype and o.stride(1) == 1 and out.stride(1) == 1 and gate.stride(1) == 1
+    assert weight.dtype == torch.float32 and weight.numel() == vdim and weight.is_contiguous()
+    _check(core().le_head_norm_gate(_ptr(out), out.stride(0), _ptr(o), o.stride(0), _ptr(gate), gate.stride(0),
+                                    dtype_code(out.dtype), _ptr(weight), float(eps), T, heads, vdim, _stream()),
+           "le_head_norm_gate")
+
+
+# -------------------------------------------------------------------------- rotary pairs with a norm per head
+def rope_norm_store(rows, k_cache, v_cache, rates, positions, request_of_token, block_table, heads, kv_heads, head_dim,
+                    rot_col, rot, unit_eps, norm_dim, page_size, write_kv, values_are_keys, status) -> None:
+    """Rows hold query heads, then key heads, ``head_dim`` entries each.  The
+    entries (rot_col + 2i, rot_col + 2i + 1) below rot_col + ``rot`` of every
+    head turn by position * rates[i]; with ``unit_eps`` not None the head is
+    then divided by sqrt(mean over its first ``norm_dim`` entries of x^2 +
+    unit_eps).  Queries are rewritten in place, keys go to ``k_cache``, and
+    ``v_cache`` receives the keys as they were projected when
+    ``values_are_keys``.  ``write_kv`` False: the queries only."""
+    _need_cuda(rows, k_cache, v_cache, rates, positions, block_table)
+    T = rows.shape[0]
+    assert rows.stride(1) == 1 and rows.shape[1] >= (heads + (kv_heads if write_kv else 0)) * head_dim
+    assert rates.dtype == torch.float32 and rates.is_contiguous() and rates.numel() >= rot // 2
+    pages = 0
+    if write_kv:
+        assert k_cache.dtype == rows.dtype and k_cache.is_contiguous()
+        assert tuple(k_cache.shape[1:]) == (kv_heads, page_size, head_dim)
+        assert not values_are_keys or (v_cache.shape == k_cache.shape and v_cache.is_contiguous())
+        pages = k_cache.shape[0]
+    _check(core().le_rope_norm_store(_ptr(rows), rows.stride(0), dtype_code(rows.dtype), _ptr(k_cache) if write_kv else None,
+                                     _ptr(v_cache) if write_kv and values_are_keys else None, _ptr(rates), _ptr(positions),
+                                     _ptr(request_of_token), _ptr(block_table), block_table.shape[1], T, heads, kv_heads,
+                                     head_dim, rot_col, rot, 0 if unit_eps is None else 1,
+                                     0.0 if unit_eps is None else float(unit_eps), norm_dim, page_size, pages,
+                                     1 if write_kv else 0, 1 if values_are_keys else 0, _ptr(status), _stream()),
+           "le_rope_norm_store")
+
+
+def latent_rope_store(src, col, rank, rot, padded, weight, eps, rates, cache, positions, request_of_token, block_table,
+                      page_size, status, second=None) -> None:
+    """The latent at columns [col, col + rank) of ``src`` is normed (weight
+    [rank]) and the ``rot`` columns behind it are turned in neighbouring pairs
+    by position * rates[i]; both go to ``cache`` [pages, 1, page, padded]
+    (None: nothing is stored).  ``second`` = (col2, rank2, weight2, out2): a
+    second latent of the row is normed into ``out2``."""
+    _need_cuda(src, weight, rates, cache, positions, block_table)
+    T = src.shape[0]
+    assert src.stride(1) == 1 and weight.dtype == torch.float32 and weight.numel() == rank
+    assert rot == 0 or (rates is not None and rates.dtype == torch.float32 and rates.numel() >= rot // 2)
+    pages = 0
+    if cache is not None:
+        assert cache.dtype == src.dtype and cache.is_contiguous() and tuple(cache.shape[1:]) == (1, page_size, padded)
+        pages = cache.shape[0]
+    col2, rank2, weight2, out2 = second if second is not None else (0, 0, None, None)
+    if out2 is not None:
+        assert out2.dtype == src.dtype and out2.stride(1) == 1 and weight2.dtype == torch.float32 and weight2.numel() == rank2
+    _check(core().le_latent_rope_store(_ptr(src), src.stride(0), dtype_code(src.dtype), col, rank, rot, padded, _ptr(weight),
+                                       float(eps), _ptr(rates), _ptr(cache), col2, rank2, _ptr(weight2), _ptr(out2),
+                                       out2.stride(0) if out2 is not None else 0, _ptr(positions), _ptr(request_of_token),
+                                       _ptr(block_table), block_table.shape[1], T, page_size, pages, _ptr(status), _stream()),
+           "le_latent_rope_store")
+
+
+# -------------------------------------------------------------------------- sub-layers side by side; inputs per token
+def _addend(t, rows: int, width: int):
+    """(pointer, dtype code, partial sums, elements between them) of a
+    sub-layer's output on its way into the stream: [rows, width] in the
+    activations' type or float32, or float32 partial sums [parts, rows, width]."""
+    if t is None:
+        return None, F32, 1, 0
+    assert t.is_contiguous() and tuple(t.shape[-2:]) == (rows, width)
+    if t.dim() == 3:
+        assert t.dtype == torch.float32
+        return t.data_ptr(), F32, t.shape[0], t.stride(0)
+    return t.data_ptr(), dtype_code(t.dtype), 1, 0
+
+
+def rmsnorm_pair(out1, out2, resid, w1, w2, eps, addend=None, addend_weight=None, addend_eps: float = 0.0, rows=None) -> None:
+    """``addend`` first enters the 32-bit stream ``resid`` [T, W]: plainly, or,
+    with ``addend_weight`` [W], as addend / sqrt(mean(addend^2) + addend_eps) *
+    addend_weight.  Then out1 = rmsnorm(resid) * w1 and (``out2`` given) out2 =
+    rmsnorm(resid) * w2.  ``out1`` None: only the addend enters.  With ``rows``
+    only those rows are normed and ``resid`` is left as it is."""
+    _need_cuda(out1, out2, resid, w1, w2, addend, addend_weight, rows)
+    T, W = resid.shape
+    assert resid.dtype == torch.float32 and resid.is_contiguous()
+    n = T if rows is None else (out1.shape[0] if out1 is not None else 0)
+    for o, w in ((out1, w1), (out2, w2)):
+        if o is not None:
+            assert o.is_contiguous() and o.shape == (n, W) and w.dtype == torch.float32 and w.numel() == W
+    ptr, code, parts, stride = _addend(addend, T, W)
+    out_code = dtype_code(out1.dtype) if out1 is not None else F32
+    _check(core().le_rmsnorm_pair(_ptr(out1), _ptr(out2), out_code, _ptr(resid), ptr, code, parts, stride,
+                                  _ptr(addend_weight), float(addend_eps), _ptr(w1), _ptr(w2), float(eps), _ptr(rows), n, W,
+                                  _stream()), "le_rmsnorm_pair")
+
+
+def residual_add(resid, a=None, f=None, bias=None, copy=None) -> None:
+    """resid += a + f + bias (each optional; a and f as _addend() takes them,
+    bias float32 [W]); ``copy`` receives the new rows in its own type."""
+    _need_cuda(resid, a, f, bias, copy)
+    T, W = resid.shape
+    assert resid.dtype == torch.float32 and resid.is_contiguous()
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == W)
+    assert copy is None or (copy.is_contiguous() and copy.shape == resid.shape)
+    ap, ac, an, as_ = _addend(a, T, W)
+    fp, fc, fn, fs = _addend(f, T, W)
+    _check(core().le_residual_add(_ptr(resid), _ptr(copy), dtype_code(copy.dtype) if copy is not None else F32, ap, ac, an,
+                                  as_, fp, fc, fn, fs, _ptr(bias), T, W, _stream()), "le_residual_add")
+
+
+def gate_rows(out, z, table, col, ids, status) -> None:
+    """out[t, j] = gelu_tanh(z[t, j]) * table[ids[t], col + j]."""
+    _need_cuda(out, z, table, ids)
+    T, D = z.shape
+    assert out.shape == z.shape and out.dtype == z.dtype and out.is_contiguous() and z.is_contiguous()
+    assert table.stride(1) == 1 and 0 <= col and col + D <= table.shape[1] and ids.dtype == torch.int32
+    _check(core().le_gate_rows(_ptr(out), _ptr(z), dtype_code(z.dtype), _ptr(table), dtype_code(table.dtype), table.stride(0),
+                               col, _ptr(ids), table.shape[0], T, D, _ptr(status), _stream()), "le_gate_rows")
+
+
+def stream_entry(resid, table, ids, vec, status) -> None:
+    """resid[t] += table[ids[t]] + vec (either may be None)."""
+    _need_cuda(resid, table, ids, vec)
+    T, W = resid.shape
+    assert resid.dtype == torch.float32 and resid.is_contiguous()
+    assert table is None or (table.is_contiguous() and table.shape[1] == W)
+    assert vec is None or (vec.dtype == torch.float32 and vec.is_contiguous() and vec.numel() == W)
+    _check(core().le_stream_entry(_ptr(resid), _ptr(table), dtype_code(table.dtype) if table is not None else F32, _ptr(ids),
+                                  table.shape[0] if table is not None else 0, _ptr(vec), T, W, _ptr(status), _stream()),
+           "le_stream_entry")

@@ -22,7 +22,11 @@ What a description may choose beyond the reference's Llama layer:
 * ``position`` None: queries and keys are used as projected;
 * ``gate_name``: a tensor [nh, H]; head h's output is multiplied by
   sigmoid(gate_h . x) before the output projection (the gate's rows ride at
-  the end of the fused projection).
+  the end of the fused projection);
+* ``v_name`` None: there is no value projection, the values are the keys as
+  projected (before any position encoding or norm of the keys); the position
+  encoding then fills the value pool itself (it is built with
+  ``values_are_keys=True``).
 
 The reference runs attention two ways, FlashAttention on the step's own keys
 for a whole prompt and PagedAttention for one decoded token
@@ -71,16 +75,23 @@ def signed_scale(scale: float, head_scale: torch.Tensor | None, num_heads: int, 
 @register_mixer("attention")
 class AttentionMixer(Mixer):
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, position: PartSpec | None,
-                 q_name: str, k_name: str, v_name: str, o_name: str, window: int | None = None,
+                 q_name: str, k_name: str, v_name: str | None, o_name: str, window: int | None = None,
                  chunk: int | None = None, scale: float | None = None, value_dim: int | None = None,
                  head_scale_name: str | None = None, gate_name: str | None = None):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads do not divide into {num_kv_heads} groups")
         self.qk_dim = int(head_dim)
         self.value_dim = int(value_dim) if value_dim else self.qk_dim
+        self.values_are_keys = v_name is None
+        if self.values_are_keys and (position is None or self.value_dim != self.qk_dim):
+            raise ValueError("values that are the keys need a position encoding that stores them, and the keys' size")
         # the one head size of kernels and pages
         self.head_dim = (max(self.qk_dim, self.value_dim) + 15) // 16 * 16
-        if position is not None and self.head_dim != self.qk_dim:
+        self.position = None
+        if position is not None:
+            self.position = (POSITION_ENCODINGS.build(position, values_are_keys=True) if self.values_are_keys
+                             else POSITION_ENCODINGS.build(position))
+        if position is not None and self.head_dim != self.qk_dim and not getattr(self.position, "padded_heads_ok", False):
             raise ValueError(f"a position encoding needs a query/key size that is a multiple of 16 and not below the "
                              f"value size, got {head_dim} and {self.value_dim}")
         if position is not None and gate_name:
@@ -96,7 +107,6 @@ class AttentionMixer(Mixer):
         self.names = (q_name, k_name, v_name, o_name)
         self.head_scale_name, self.gate_name = head_scale_name, gate_name
         self.gate_rows = (self.num_heads + 7) // 8 * 8 if gate_name else 0      # rows of the projection stay 16-byte multiples
-        self.position = POSITION_ENCODINGS.build(position) if position is not None else None
         self.w_qkv = self.w_o = self.head_scale = None
         self.head_scale_positive = True
         self.runtime = None
@@ -117,7 +127,9 @@ class AttentionMixer(Mixer):
         q, k, v, o = self.names
         H, nh, nkv = self.hidden_size, self.num_heads, self.num_kv_heads
         decls = [TensorDecl(q, (nh * self.qk_dim, H)), TensorDecl(k, (nkv * self.qk_dim, H)),
-                 TensorDecl(v, (nkv * self.value_dim, H)), TensorDecl(o, (H, nh * self.value_dim))]
+                 TensorDecl(o, (H, nh * self.value_dim))]
+        if not self.values_are_keys:
+            decls.insert(2, TensorDecl(v, (nkv * self.value_dim, H)))
         if self.head_scale_name:
             decls.append(TensorDecl(self.head_scale_name, (nh,), role="vector", init="ones_jitter"))
         if self.gate_name:
@@ -127,8 +139,9 @@ class AttentionMixer(Mixer):
     def bind(self, get, runtime):
         q, k, v, o = self.names
         nh, nkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
-        rows = [pad_head_rows(get(q), nh, self.qk_dim, hd), pad_head_rows(get(k), nkv, self.qk_dim, hd),
-                pad_head_rows(get(v), nkv, self.value_dim, hd)]
+        rows = [pad_head_rows(get(q), nh, self.qk_dim, hd), pad_head_rows(get(k), nkv, self.qk_dim, hd)]
+        if not self.values_are_keys:
+            rows.append(pad_head_rows(get(v), nkv, self.value_dim, hd))
         if self.gate_name:
             gate = get(self.gate_name)
             pad = torch.zeros((self.gate_rows - nh, gate.shape[1]), dtype=gate.dtype, device=gate.device)
@@ -147,7 +160,7 @@ class AttentionMixer(Mixer):
         nh, nkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
         T = x.shape[0]
         ws = ctx.workspace
-        width = (nh + 2 * nkv) * hd
+        width = (nh + (1 if self.values_are_keys else 2) * nkv) * hd
         qkv = ws.get("qkv", (T, width + self.gate_rows), rt.dtype)
         # a position encoding may know how to run the product itself, with its own work in the epilogue
         fused = getattr(self.position, "product_encode_store", None) if not self.gate_rows else None

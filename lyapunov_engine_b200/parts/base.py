@@ -41,6 +41,12 @@ Interfaces (all tensors are CUDA tensors; T tokens in the step, H width):
     the norm before it and itself as one kernel where it can (None: it cannot).
 ``FeedForward``
     ``forward(x, ctx) -> y``.
+``StreamInput``
+    ``forward(stream, ctx)``: adds something to the residual stream that
+    depends on the step's token ids or on nothing but learned vectors (an
+    embedding per layer behind a gate, what a pass over a stretch of layers adds
+    before its first layer).  A block may run one after its sub-layers; a
+    ``RunSpec`` may name one that runs before its layer.
 ``Block``
     ``forward(stream, ctx, cache)``: arranges norms, mixer and feed-forward
     around the residual stream (``stream.resid`` 32-bit plus a ``pending``
@@ -76,9 +82,12 @@ class LayerSpec:
 class RunSpec:
     """One entry of the run order: run ``layer``; ``reads_cache_of`` names an
     earlier entry (by its index in the run order) whose cache this run reads
-    instead of writing one of its own."""
+    instead of writing one of its own; ``entry``: a stream input that runs
+    right before the layer (what a pass over a stretch of layers adds before its
+    first one)."""
     layer: int
     reads_cache_of: int | None = None
+    entry: PartSpec | None = None
 
 
 @dataclass(frozen=True)
@@ -176,6 +185,12 @@ class Mixer(Part):
     def state_need(self) -> StateNeed | None:
         return None
 
+    def extra_state_needs(self) -> dict[str, "StateNeed"]:
+        """More per-request state than the one buffer of ``state_need()``, by
+        names of the mixer's choosing; the block lists them among its own
+        (``Block.extra_state_needs()``) and ``cache.extra[name]`` holds each."""
+        return {}
+
     def tile_sizes(self) -> list[int]:
         """Query-tile sizes its kernels want: for each, ``ctx.tiles[size]`` lists
         (request of each tile, first query token of the tile within the
@@ -212,14 +227,33 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class StreamInput(Part):
+    # True: forward() wants the stream's rows in the activations' type (``copy``), for a product that reads them
+    reads_stream = False
+
+    def forward(self, stream, ctx, copy=None) -> None:
+        raise NotImplementedError
+
+
+class NormedAddend:
+    """How a pending output enters the stream when it is normed on the way:
+    resid += pending / sqrt(mean(pending^2) + eps) * weight (weight [W],
+    32-bit).  A norm that reads such a stream applies it in its own kernel."""
+    __slots__ = ("weight", "eps")
+
+    def __init__(self, weight, eps: float):
+        self.weight, self.eps = weight, float(eps)
+
+
 class Block(Part):
     mixer: Mixer
 
     def extra_state_needs(self) -> dict[str, StateNeed]:
-        """Per-request state that parts of the block other than the mixer keep,
-        by a name of the block's choosing; ``cache.extra[name]`` holds each
-        buffer when the block runs (rows by state slot, as the mixer's)."""
-        return {}
+        """Per-request state that parts of the block other than the mixer keep
+        (and what the mixer keeps beyond its one buffer), by a name of the
+        block's choosing; ``cache.extra[name]`` holds each buffer when the
+        block runs (rows by state slot, as the mixer's)."""
+        return dict(self.mixer.extra_state_needs())
 
     def tile_sizes(self) -> list[int]:
         return list(self.mixer.tile_sizes())
@@ -233,8 +267,9 @@ class ResidualStream:
     that has not entered it yet (the next norm adds it).  ``resid`` is [T, W],
     or [T, copies, W] where a block arrangement keeps several copies of the
     stream; ``update`` says how ``pending`` enters: None: resid += pending;
-    else a ``StreamLink`` whose ``mix`` [copies, copies] and ``post`` [copies]
-    give copy j <- sum_s mix[s, j] copy_s + post[j] * pending."""
+    a ``StreamLink`` whose ``mix`` [copies, copies] and ``post`` [copies]
+    give copy j <- sum_s mix[s, j] copy_s + post[j] * pending; a
+    ``NormedAddend``: resid += pending normed with a weight."""
     __slots__ = ("resid", "pending", "update", "copies")
 
     def __init__(self, resid, pending=None):
@@ -274,6 +309,7 @@ POSITION_ENCODINGS = Registry("position encoding")
 MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
 INPUT_FILTERS = Registry("input filter")
+STREAM_INPUTS = Registry("stream input")
 BLOCKS = Registry("block arrangement")
 EMBEDDINGS = Registry("embedding")
 HEADS = Registry("output head")
@@ -283,6 +319,7 @@ register_position_encoding = POSITION_ENCODINGS.register
 register_mixer = MIXERS.register
 register_feed_forward = FEED_FORWARDS.register
 register_input_filter = INPUT_FILTERS.register
+register_stream_input = STREAM_INPUTS.register
 register_block = BLOCKS.register
 register_embedding = EMBEDDINGS.register
 register_head = HEADS.register

@@ -10,10 +10,13 @@ block, or the final one) adds it.  Two options: ``mixer_input``, an input
 filter between the first norm and the mixer (h = filter(norm1(h)) is what the
 mixer reads), and a block without a feed-forward (``feed_forward`` None: only
 the first line above).
+
+"parallel": both sub-layers read the same stream (see ``ParallelBlock``).
 """
 from __future__ import annotations
 
-from .base import BLOCKS, FEED_FORWARDS, INPUT_FILTERS, MIXERS, NORMS, Block, PartSpec, register_block
+from .. import ops
+from .base import BLOCKS, FEED_FORWARDS, INPUT_FILTERS, MIXERS, NORMS, STREAM_INPUTS, Block, PartSpec, register_block
 
 
 @register_block("prenorm")
@@ -33,8 +36,11 @@ class PreNormBlock(Block):
                 if p is not None]
 
     def extra_state_needs(self):
+        needs = dict(self.mixer.extra_state_needs())
         need = self.mixer_input.state_need() if self.mixer_input is not None else None
-        return {"mixer_input": need} if need is not None else {}
+        if need is not None:
+            needs["mixer_input"] = need
+        return needs
 
     def tile_sizes(self):
         return list(self.mixer.tile_sizes()) + (self.mixer_input.tile_sizes() if self.mixer_input is not None else [])
@@ -65,3 +71,52 @@ class PreNormBlock(Block):
             return
         n = self.feed_forward_norm.apply(stream.resid, a, workspace=ctx.workspace)
         stream.pending = self.feed_forward.forward(n, ctx)
+
+
+@register_block("parallel")
+class ParallelBlock(Block):
+    """The mixer and the feed-forward read the same stream, each through a
+    norm of its own, and their outputs enter together:
+        h = h + (mixer(norm1(h)) + feed_forward(norm2(h)))
+    (one kernel makes both norms; one adds both outputs, and the feed-forward's
+    output bias, in 32 bits).  ``after``: a stream input that runs on the new
+    h, after the sub-layers (an embedding per token behind a gate, say); what
+    it leaves pending enters in the next norm's kernel."""
+
+    def __init__(self, mixer: PartSpec, feed_forward: PartSpec | None, mixer_norm: PartSpec,
+                 feed_forward_norm: PartSpec | None, after: PartSpec | None = None):
+        if (feed_forward is None) != (feed_forward_norm is None):
+            raise ValueError("a block has a feed-forward and its norm, or neither")
+        self.mixer = MIXERS.build(mixer)
+        self.feed_forward = FEED_FORWARDS.build(feed_forward) if feed_forward is not None else None
+        self.mixer_norm = NORMS.build(mixer_norm)
+        self.feed_forward_norm = NORMS.build(feed_forward_norm) if feed_forward_norm is not None else None
+        self.after = STREAM_INPUTS.build(after) if after is not None else None
+        if not hasattr(self.mixer_norm, "apply_pair"):
+            raise ValueError("the parallel arrangement needs norms that run as a pair (rmsnorm)")
+
+    def parts(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward, self.after)
+                if p is not None]
+
+    def tensors(self):
+        return [d for p in self.parts() for d in p.tensors()]
+
+    def bind(self, get, runtime):
+        self.runtime = runtime
+        for p in self.parts():
+            p.bind(get, runtime)
+
+    def forward(self, stream, ctx, cache) -> None:
+        n1, n2 = self.mixer_norm.apply_pair(stream, self.feed_forward_norm, workspace=ctx.workspace)
+        a = self.mixer.forward(n1, ctx, cache)
+        f = bias = None
+        if self.feed_forward is not None:
+            f = self.feed_forward.forward(n2, ctx)
+            bias = getattr(self.feed_forward, "output_bias", None)     # (a bias the feed-forward leaves to the addition)
+        copy = None
+        if self.after is not None and getattr(self.after, "reads_stream", False):
+            copy = ctx.workspace.get("stream_copy", tuple(stream.resid.shape), self.runtime.dtype)
+        ops.residual_add(stream.resid, a, f, bias, copy)
+        if self.after is not None:
+            self.after.forward(stream, ctx, copy)

@@ -9,17 +9,24 @@ are bare parameters of the decoder layer (python/lyapunov_engine/models/llama.py
 from __future__ import annotations
 
 from .. import ops
-from .base import Norm, TensorDecl, register_norm
+from .base import Norm, NormedAddend, TensorDecl, register_norm
 
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
     """``groups`` > 1: the row is cut into that many equal consecutive parts,
-    each divided by its own sqrt(mean(part^2) + eps), before the weight."""
+    each divided by its own sqrt(mean(part^2) + eps), before the weight.
+    ``offset`` c: the stored weight lies around zero and the factor is c + w
+    (made once at load, in 32 bits).
 
-    def __init__(self, hidden_size: int, eps: float, weight_name: str, groups: int = 1):
+    It also reads a stream whose pending output enters normed
+    (``NormedAddend``), and two such norms of the same stream run as one kernel
+    (``apply_pair``: sub-layers that read the stream side by side)."""
+
+    def __init__(self, hidden_size: int, eps: float, weight_name: str, groups: int = 1, offset: float = 0.0):
         self.hidden_size = int(hidden_size)
         self.groups = int(groups)
+        self.offset = float(offset)
         if self.groups < 1 or self.hidden_size % self.groups:
             raise ValueError(f"a norm over {hidden_size} values cannot be cut into {groups} equal parts")
         self.eps = float(eps)
@@ -28,10 +35,13 @@ class RMSNorm(Norm):
         self.runtime = None
 
     def tensors(self):
-        return [TensorDecl(self.weight_name, (self.hidden_size,), role="vector", init="ones_jitter")]
+        return [TensorDecl(self.weight_name, (self.hidden_size,), role="vector",
+                           init="taps" if self.offset else "ones_jitter")]
 
     def bind(self, get, runtime):
         self.weight = get(self.weight_name)
+        if self.offset:
+            self.weight = (self.weight + self.offset).contiguous()
         self.runtime = runtime
 
     def apply(self, resid, delta=None, rows=None, workspace=None, key="normed"):
@@ -40,6 +50,31 @@ class RMSNorm(Norm):
         out = ws.get(key, (n, self.hidden_size), self.runtime.dtype)
         ops.rmsnorm(out, resid, delta, self.weight, self.eps, rows, groups=self.groups)
         return out
+
+    def apply_stream(self, stream, read=None, rows=None, workspace=None, key="normed"):
+        if not isinstance(stream.update, NormedAddend):
+            return super().apply_stream(stream, read, rows, workspace, key)
+        return self.apply_pair(stream, None, rows=rows, workspace=workspace, keys=(key, None))[0]
+
+    def apply_pair(self, stream, other: "RMSNorm | None", rows=None, workspace=None, keys=("normed", "normed_2")):
+        """(this norm's output, ``other``'s) of the same stream, whose pending
+        output enters first, plainly or normed, in one kernel.  Without
+        ``rows`` the pending output is consumed."""
+        if stream.copies != 1 or self.groups != 1 or (other is not None and (other.groups != 1 or other.eps != self.eps)):
+            raise ValueError("norms that run as a pair read one copy of the stream, whole rows, with one eps")
+        update = stream.update
+        if update is not None and not isinstance(update, NormedAddend):
+            raise ValueError(f"{type(self).__name__} cannot apply a pending {type(update).__name__}")
+        n = stream.resid.shape[0] if rows is None else rows.shape[0]
+        ws = workspace or self.runtime.workspace
+        out1 = ws.get(keys[0], (n, self.hidden_size), self.runtime.dtype)
+        out2 = ws.get(keys[1], (n, self.hidden_size), self.runtime.dtype) if other is not None else None
+        ops.rmsnorm_pair(out1, out2, stream.resid, self.weight, other.weight if other is not None else None, self.eps,
+                         addend=stream.pending, addend_weight=update.weight if update is not None else None,
+                         addend_eps=update.eps if update is not None else 0.0, rows=rows)
+        if rows is None:
+            stream.pending = stream.update = None
+        return out1, out2
 
 
 @register_norm("layernorm")

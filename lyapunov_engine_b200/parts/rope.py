@@ -96,3 +96,52 @@ class RotaryEncoding(PositionEncoding):
         ops.rope_kv_write(qkv, kv.k if kv is not None else None, kv.v if kv is not None else None, self.table,
                           ctx.positions, ctx.request_of_token, ctx.block_tables[kv.group] if kv is not None else ctx.block_tables[0],
                           nh, nkv, hd, kv.page_size if kv is not None else 1, write and kv is not None, ctx.status)
+
+
+def pair_rates(rot: int, base: float) -> torch.Tensor:
+    """f_i = base^(-2i / rot), i < rot / 2: made in 64 bits, kept as float32."""
+    i = torch.arange(0, rot, 2, dtype=torch.float64)
+    return torch.pow(torch.tensor(float(base), dtype=torch.float64), -i / max(rot, 1)).to(torch.float32)
+
+
+@register_position_encoding("rotary_pairs")
+class RotaryPairsEncoding(PositionEncoding):
+    """Rotary positions on neighbouring entries: in every head of queries and
+    keys the pair (2i, 2i + 1), 2i + 1 < ``rot``, turns by the angle p * f_i,
+    f_i = base^(-2i / rot): (a, b) -> (a cos - b sin, b cos + a sin); the
+    entries from ``rot`` on pass unchanged.  ``unit_eps`` not None: after the
+    turn every head of queries and keys is divided by sqrt(mean(head^2) +
+    unit_eps) (a norm without a weight).  ``values_are_keys``: the projection
+    has no values of its own; the value pool receives the keys as projected,
+    before turn and norm.  No table: the angle (position times rate), sine and
+    cosine are computed in 32 bits from the step's own positions, so there is no
+    longest position.  ``head_dim`` is the real size of queries and keys; the
+    heads the kernels see may be padded with zeros behind it."""
+    padded_heads_ok = True
+
+    def __init__(self, head_dim: int, rot: int, base: float, unit_eps: float | None = None, values_are_keys: bool = False):
+        self.head_dim, self.rot, self.base = int(head_dim), int(rot), float(base)
+        if self.rot % 2 or not 0 <= self.rot <= self.head_dim:
+            raise ValueError(f"rotary width {rot} must be even and at most the head size {head_dim}")
+        self.unit_eps = float(unit_eps) if unit_eps is not None else None
+        self.values_are_keys = bool(values_are_keys)
+        self.rates = None
+
+    def bind(self, get, runtime):
+        key = ("rotary_pairs", self.rot, self.base)
+        rates = runtime.shared.get(key)
+        if rates is None:
+            rates = runtime.shared[key] = pair_rates(max(self.rot, 2), self.base).to(runtime.device).contiguous()
+        self.rates = rates
+
+    def encode_and_store(self, qkv, geometry, ctx, kv, write: bool) -> None:
+        nh, nkv, hd = geometry
+        write = write and kv is not None
+        ops.rope_norm_store(qkv, kv.k if write else None, kv.v if write else None, self.rates, ctx.positions,
+                            ctx.request_of_token, ctx.block_tables[kv.group] if kv is not None else ctx.block_tables[0],
+                            nh, nkv, hd, 0, self.rot, self.unit_eps, self.head_dim, kv.page_size if kv is not None else 1,
+                            write, self.values_are_keys, ctx.status)
+        if write and not self.values_are_keys:
+            # (values of their own: stored as projected; the store kernel writes two pools, both are the values' here)
+            ops.kv_store(qkv, (nh + nkv) * hd, (nh + nkv) * hd, kv.v, kv.v, ctx.positions, ctx.request_of_token,
+                         ctx.block_tables[kv.group], nkv, hd, kv.page_size, ctx.status)
