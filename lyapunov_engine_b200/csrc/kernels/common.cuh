@@ -166,11 +166,19 @@ __device__ __forceinline__ float fast_exp2(float x) {
 //   kind 0: silu(g) * u
 //   kind 1: g' = min(g, limit), u' = clamp(u, -limit, limit); g' * sigmoid(slope * g') * (u' + 1)
 //   kind 2: max(g, 0) * u
+// `bias` (float32 [2 * inter], the gate's entries first, or null): what a
+// product's epilogue adds to column n of g (bias[n]) and of u (bias[inter + n])
+// before the activation (gated_bias()).
 struct GatedActivation {
   int kind = 0;
   float slope = 1.0f;
   float limit = 0.0f;
+  const float *bias = nullptr;
+  int inter = 0;
 };
+__device__ __forceinline__ void gated_bias(float &g, float &u, int n, const GatedActivation &a) {
+  if (a.bias != nullptr) g += a.bias[n], u += a.bias[a.inter + n];
+}
 template <bool FAST_EXP = false>
 __device__ __forceinline__ float gated_activation(float g, float u, const GatedActivation &a) {
   if (a.kind == 1) {

@@ -309,7 +309,11 @@ gemm_skinny_kernel(TO *__restrict__ out, const bf16 *__restrict__ x, const bf16 
       const int row = m * 8 + 2 * t + (e & 1);
       if (n < n_out && row < M) {
         float x = v[0];
-        if constexpr (GATED) x = le::gated_activation(x, v[WSETS - 1], act);
+        if constexpr (GATED) {
+          float u = v[WSETS - 1];
+          le::gated_bias(x, u, n, act);
+          x = le::gated_activation(x, u, act);
+        }
         dst[row * ldo + n] = le::from_f32<TO>(x);
       }
     }
@@ -435,9 +439,21 @@ int dispatch_m(void *out, const void *x, const void *w, int M, int N, int K, int
 // gated = 1: W is [N = 2 I, K], out is bfloat16 [M, I] = act(x Wg^T, x Wu^T) with the activation
 // (act_kind, act_slope, act_limit) of le::GatedActivation (0: silu(g) * u); splits must be 1.
 // Needs M <= 64, K a multiple of 8, 16-byte aligned rows of x and W.
+LE_API int le_gemm_skinny_bias_bf16(void *out, int out_dtype, const void *x, const void *w, int M, int N, int K, int64_t ldx,
+                                    int64_t ldw, int64_t ldo, int splits, int64_t split_stride, int gated, int act_kind,
+                                    float act_slope, float act_limit, const float *bias, cudaStream_t stream);
 LE_API int le_gemm_skinny_bf16(void *out, int out_dtype, const void *x, const void *w, int M, int N, int K, int64_t ldx,
                                int64_t ldw, int64_t ldo, int splits, int64_t split_stride, int gated, int act_kind,
                                float act_slope, float act_limit, cudaStream_t stream) {
+  return le_gemm_skinny_bias_bf16(out, out_dtype, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, gated, act_kind,
+                                  act_slope, act_limit, nullptr, stream);
+}
+
+// The same; in the gated form `bias` (float32 [N], the gate's entries first, or null) is added to the product's
+// columns before the activation.
+LE_API int le_gemm_skinny_bias_bf16(void *out, int out_dtype, const void *x, const void *w, int M, int N, int K, int64_t ldx,
+                                    int64_t ldw, int64_t ldo, int splits, int64_t split_stride, int gated, int act_kind,
+                                    float act_slope, float act_limit, const float *bias, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 64) return le::invalid("le_gemm_skinny_bf16: at most 64 rows, got %d", M);
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8) return le::invalid("le_gemm_skinny_bf16: K (%d) and the leading dimensions must be multiples of 8", K);
@@ -445,7 +461,8 @@ LE_API int le_gemm_skinny_bf16(void *out, int out_dtype, const void *x, const vo
   if (gated) {
     if (splits != 1 || out_dtype != LE_BF16 || N % 2) return le::invalid("le_gemm_skinny_bf16: the gated form has one split, bfloat16 output and an even N");
     if (act_kind < 0 || act_kind > 2) return le::invalid("le_gemm_skinny_bf16: unknown activation %d", act_kind);
-    return dispatch_m<true, bf16>(out, x, w, M, N, K, ldx, ldw, ldo, 1, 0, stream, le::GatedActivation{act_kind, act_slope, act_limit});
+    return dispatch_m<true, bf16>(out, x, w, M, N, K, ldx, ldw, ldo, 1, 0, stream,
+                                  le::GatedActivation{act_kind, act_slope, act_limit, bias, N / 2});
   }
   if (splits > 1 && out_dtype != LE_F32) return le::invalid("le_gemm_skinny_bf16: partial sums of a split K are float32");
   if (out_dtype == LE_F32) return dispatch_m<false, float>(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream);

@@ -280,7 +280,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               f[i] = __uint_as_float(v[j + i]);
-              if (GATED) f[i] = le::gated_activation<true>(f[i], __uint_as_float(u[j + i]), act);
+              if (GATED) {
+                float up = __uint_as_float(u[j + i]);
+                if (col + i < n_limit) le::gated_bias(f[i], up, col + i, act);
+                f[i] = le::gated_activation<true>(f[i], up, act);
+              }
             }
             if (col + 8 <= n_limit && (reinterpret_cast<uintptr_t>(dst + col) & 15) == 0) {
               if constexpr (sizeof(TO) == 2) {
@@ -408,12 +412,24 @@ int launch(void *out, const void *x, const void *w, int M, int N, int K, int64_t
 // act(x Wg^T, x Wu^T) with the activation (act_kind, act_slope, act_limit) of
 // le::GatedActivation (0: silu(g) * u).  Needs K and the leading dimensions of x and W to
 // be multiples of 8 and their base addresses 16-byte aligned (TMA).
+LE_API int le_gemm_tc_bias_bf16(void *out, int out_dtype, const void *x, const void *w, int M, int N, int K, int64_t ldx,
+                                int64_t ldw, int64_t ldo, int gated, int act_kind, float act_slope, float act_limit,
+                                const float *bias, int *status, cudaStream_t stream);
 LE_API int le_gemm_tc_bf16(void *out, int out_dtype, const void *x, const void *w, int M, int N, int K, int64_t ldx, int64_t ldw,
                            int64_t ldo, int gated, int act_kind, float act_slope, float act_limit, int *status,
                            cudaStream_t stream) {
+  return le_gemm_tc_bias_bf16(out, out_dtype, x, w, M, N, K, ldx, ldw, ldo, gated, act_kind, act_slope, act_limit, nullptr,
+                              status, stream);
+}
+
+// The same; in the gated form `bias` (float32 [N], the gate's entries first, or null) is added to the product's
+// columns before the activation.
+LE_API int le_gemm_tc_bias_bf16(void *out, int out_dtype, const void *x, const void *w, int M, int N, int K, int64_t ldx,
+                                int64_t ldw, int64_t ldo, int gated, int act_kind, float act_slope, float act_limit,
+                                const float *bias, int *status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (act_kind < 0 || act_kind > 2) return le::invalid("le_gemm_tc_bf16: unknown activation %d", act_kind);
-  const le::GatedActivation act{act_kind, act_slope, act_limit};
+  const le::GatedActivation act{act_kind, act_slope, act_limit, gated ? bias : nullptr, N / 2};
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8) return le::invalid("le_gemm_tc_bf16: K (%d) and the leading dimensions must be multiples of 8", K);
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return le::invalid("le_gemm_tc_bf16: x and W must be 16-byte aligned");
   // pairs of SMs on 256 x 256 tiles where those give at least half of the pairs a tile and the second block of a

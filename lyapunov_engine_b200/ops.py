@@ -114,6 +114,10 @@ _CORE_SIGNATURES = {
                         c_int, c_float, c_float, c_void_p, c_void_p],
     "le_gemm_skinny_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int,
                             c_int64, c_int, c_int, c_float, c_float, c_void_p],
+    "le_gemm_skinny_bias_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int,
+                                 c_int64, c_int, c_int, c_float, c_float, c_void_p, c_void_p],
+    "le_gemm_tc_bias_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int,
+                             c_int, c_float, c_float, c_void_p, c_void_p, c_void_p],
     "le_gemm_skinny_rotary_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p,
                                    c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                    c_int, c_void_p, c_void_p],
@@ -567,23 +571,25 @@ def skinny_applies(a: torch.Tensor, w: torch.Tensor, rows: int | None = None) ->
 
 
 def gemm_skinny(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, splits: int = 1, gated: bool = False,
-                activation=(0, 1.0, 0.0)) -> None:
+                activation=(0, 1.0, 0.0), bias=None) -> None:
     """The package's weight-streaming product for at most 64 rows (bfloat16
     inputs).  ``splits`` > 1: ``out`` is float32 [splits, M, N] partial sums.
     ``gated``: ``w`` is [2 I, K] (gate rows, then up rows), out = act(gate, up)
-    with ``activation`` = (kind, slope, limit) as glu() takes them (silu(gate) * up by default)."""
-    _need_cuda(out, a, w)
+    with ``activation`` = (kind, slope, limit) as glu() takes them (silu(gate) * up by default), and
+    ``bias`` (float32 [2 I] or None) added to the product's columns before it."""
+    _need_cuda(out, a, w, bias)
     M, K = a.shape
     N = w.shape[0]
+    assert bias is None or (gated and bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == N)
     if splits > 1:
         assert out.dtype == torch.float32 and out.shape == (splits, M, N) and out.is_contiguous()
         ldo, stride = N, out.stride(0)
     else:
         assert out.shape[-2:] == (M, N // 2 if gated else N) and out.stride(-1) == 1
         ldo, stride = out.stride(-2), 0
-    _check(core().le_gemm_skinny_bf16(_ptr(out), dtype_code(out.dtype), _ptr(a), _ptr(w), M, N, K, a.stride(0),
-                                      w.stride(0), ldo, splits, stride, 1 if gated else 0, int(activation[0]),
-                                      float(activation[1]), float(activation[2]), _stream()),
+    _check(core().le_gemm_skinny_bias_bf16(_ptr(out), dtype_code(out.dtype), _ptr(a), _ptr(w), M, N, K, a.stride(0),
+                                           w.stride(0), ldo, splits, stride, 1 if gated else 0, int(activation[0]),
+                                           float(activation[1]), float(activation[2]), _ptr(bias), _stream()),
            "le_gemm_skinny_bf16")
 
 
@@ -623,21 +629,23 @@ _tc_status = {}
 
 
 def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gated: bool = False, status=None,
-            activation=(0, 1.0, 0.0)) -> None:
+            activation=(0, 1.0, 0.0), bias=None) -> None:
     """The package's tcgen05 / TMA product for many rows (bfloat16 inputs):
     out = a @ w^T (bfloat16 or float32), or with ``gated`` out = act(a Wg^T,
     a Wu^T) for w = [Wg; Wu], ``activation`` = (kind, slope, limit) as glu()
-    takes them (silu(g) * u by default)."""
-    _need_cuda(out, a, w)
+    takes them (silu(g) * u by default), and ``bias`` (float32 [2 I] or None)
+    added to the product's columns before it."""
+    _need_cuda(out, a, w, bias)
     M, K = a.shape
     N = w.shape[0]
+    assert bias is None or (gated and bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == N)
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
     assert out.shape == (M, N // 2 if gated else N) and out.stride(1) == 1 and a.stride(1) == 1 and w.stride(1) == 1
     if status is None:
         status = tc_status(a.device)
-    _check(core().le_gemm_tc_bf16(_ptr(out), dtype_code(out.dtype), _ptr(a), _ptr(w), M, N, K, a.stride(0), w.stride(0),
-                                  out.stride(0), 1 if gated else 0, int(activation[0]), float(activation[1]),
-                                  float(activation[2]), _ptr(status), _stream()), "le_gemm_tc_bf16")
+    _check(core().le_gemm_tc_bias_bf16(_ptr(out), dtype_code(out.dtype), _ptr(a), _ptr(w), M, N, K, a.stride(0), w.stride(0),
+                                       out.stride(0), 1 if gated else 0, int(activation[0]), float(activation[1]),
+                                       float(activation[2]), _ptr(bias), _ptr(status), _stream()), "le_gemm_tc_bf16")
 
 
 def tc_status(device) -> torch.Tensor:
@@ -715,12 +723,22 @@ def gated_linear(out: torch.Tensor, a: torch.Tensor, w_gate_up: torch.Tensor, wo
     glu(out, gu, *activation)
 
 
+FUSE_GATED_BIAS = os.environ.get("LYAPUNOV_FUSE_GATED_BIAS", "1") not in ("0", "")
+
+
 def gated_linear_bias(out: torch.Tensor, a: torch.Tensor, w_gate_up: torch.Tensor, bias: torch.Tensor, workspace, status=None,
                       activation=(GLU_SILU, 1.0, 0.0)) -> None:
     """gated_linear() with a bias [2 I] (float32) on the product's columns
-    before the activation: the product, then the activation's kernel with the
-    bias (the sums, the bias and the activation in 32 bits where the product
-    writes 32-bit columns: few rows)."""
+    before the activation.  bfloat16: in the epilogue of the package's kernels,
+    on the 32-bit sums (weight-streaming for few rows, tcgen05 for many);
+    else the product, then the activation's kernel with the bias.
+    LYAPUNOV_FUSE_GATED_BIAS=0 takes the second way always."""
+    if FUSE_GATED_BIAS and skinny_applies(a, w_gate_up):
+        gemm_skinny(out, a, w_gate_up, gated=True, activation=activation, bias=bias)
+        return
+    if FUSE_GATED_BIAS and tc_applies(a, w_gate_up):
+        gemm_tc(out, a, w_gate_up, gated=True, status=status, activation=activation, bias=bias)
+        return
     gu = workspace.get("gate_up", (a.shape[0], w_gate_up.shape[0]), a.dtype)
     linear(gu, a, w_gate_up, status)
     glu(out, gu, *activation, bias=bias)
