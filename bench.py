@@ -1295,6 +1295,317 @@ def run_kaditar(args):
     return 0
 
 
+ZEPILIX_WINDOW = 2048       # keys a latent layer's query sees at most
+ZEPILIX_LATENT = 96         # latent size; with the turned part the cached row has 128 entries (the tensor-core kernels' largest head)
+ZEPILIX_TURNED = 32
+ZEPILIX_DELTA_HEAD = 128    # query/key and value size of a delta-rule head
+ZEPILIX_SIDE = 256          # entries of the input per token and layer
+
+
+def zepilix_config(llama: dict) -> dict:
+    """A Zepilix model with the width, feed-forward size, heads, head size, vocabulary and number of layer runs of the
+    given Llama shapes: delta rule, attention, delta rule, latent attention with a window, and so on; layers 4 to 7 run
+    twice (so four layers fewer carry weights), every layer has the input per token."""
+    nh, nkv, hd, W = llama["num_attention_heads"], llama["num_key_value_heads"], llama["head_dim"], llama["hidden_size"]
+    mlp = {"kind": "dense", "ff": llama["intermediate_size"]}
+    dh = W // ZEPILIX_DELTA_HEAD
+    delta = {"type": "delta", "mlp": mlp,
+             "mixer": {"heads": dh, "kv_heads": dh // 2, "dim": ZEPILIX_DELTA_HEAD, "vdim": ZEPILIX_DELTA_HEAD, "conv": 4}}
+    attention = {"type": "attention", "mlp": mlp,
+                 "mixer": {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+                           "rot": {"dims": hd, "base": 500000.0}}}
+    latent = {"type": "latent_attention", "mlp": mlp,
+              "mixer": {"heads": nh, "dim": hd, "rot_dim": ZEPILIX_TURNED, "vdim": hd, "kv_rank": ZEPILIX_LATENT,
+                        "q_rank": W * 3 // 8, "scale": (hd + ZEPILIX_TURNED) ** -0.5, "mask": {"size": ZEPILIX_WINDOW},
+                        "rot": {"dims": ZEPILIX_TURNED, "base": 1000000.0}}}
+    runs = llama["num_hidden_layers"]
+    looped = 4 if runs >= 12 else 0
+    kinds = (delta, attention, delta, latent)
+    cfg = {"architecture": "Zepilix", "vocab": llama["vocab_size"], "width": W, "norm": {"eps": 1e-6},
+           "token_side": {"dim": ZEPILIX_SIDE}, "layers": [kinds[i % 4] for i in range(runs - looped)]}
+    if looped:
+        cfg["loop"] = {"start": 4, "stop": 8, "times": 2}
+    return cfg
+
+
+def zepilix_runs(cfg):
+    """The layers in the order they run (a looped layer once per pass)."""
+    n = len(cfg["layers"])
+    lp = cfg.get("loop")
+    order = list(range(n)) if not lp else (list(range(lp["start"])) + list(range(lp["start"], lp["stop"])) * lp["times"]
+                                           + list(range(lp["stop"], n)))
+    return [cfg["layers"][i] for i in order]
+
+
+def zepilix_decode_bytes(cfg, batch, context):
+    """Bytes one decode step of a Zepilix model must move: the bfloat16 weights of every layer run once (a looped
+    stretch is larger than the L2, so each pass reads it again), each live request's state matrices read and written
+    (32-bit), its keys and its values' pool, or its window of cached latents."""
+    W, V, s = cfg["width"], cfg["vocab"], cfg["token_side"]["dim"]
+    total = 2 * V * W + 4 * W
+    for layer in zepilix_runs(cfg):
+        m, F = layer["mixer"], layer["mlp"]["ff"]
+        nh, d, e = m["heads"], m["dim"], m["vdim"]
+        total += 2 * 3 * F * W + 4 * (2 * F + W) + 4 * 2 * W + 2 * (2 * s * W + batch * s) + 4 * W
+        if layer["type"] == "delta":
+            G = m["kv_heads"]
+            total += 2 * ((2 * G * d + 2 * nh * e + 2 * nh) * W + W * nh * e)
+            total += batch * (2 * 4 * nh * d * e + 2 * 4 * (m["conv"] - 1) * (2 * G * d + nh * e))
+        elif layer["type"] == "attention":
+            G = m["kv_heads"]
+            total += 2 * ((nh + G) * d * W + W * nh * e) + 2 * batch * context * 2 * G * d
+        else:
+            r, t, qr = m["kv_rank"], m["rot_dim"], m["q_rank"]
+            seen = min(context, m["mask"]["size"])
+            total += 2 * ((qr + r + t) * W + nh * (d + t) * qr + nh * d * r + nh * e * r + W * nh * e) + 2 * batch * seen * (r + t)
+    return total
+
+
+def zepilix_prefill_flops(cfg, tokens):
+    """(flops of the matrix products and the attentions as computed here, flops of the delta rule's recurrence, which
+    runs on the FP32 pipes: six per entry of the state and token)."""
+    W, V, s = cfg["width"], cfg["vocab"], cfg["token_side"]["dim"]
+    flops, scan = 2 * V * W, 0
+    pairs = tokens * (tokens + 1) // 2
+    for layer in zepilix_runs(cfg):
+        m, F = layer["mixer"], layer["mlp"]["ff"]
+        nh, d, e = m["heads"], m["dim"], m["vdim"]
+        flops += 2 * tokens * (3 * F * W + 2 * s * W)
+        if layer["type"] == "delta":
+            G = m["kv_heads"]
+            flops += 2 * tokens * ((2 * G * d + 2 * nh * e + 2 * nh) * W + W * nh * e)
+            scan += 6 * tokens * nh * d * e
+        elif layer["type"] == "attention":
+            flops += 2 * tokens * ((nh + m["kv_heads"]) * d * W + W * nh * e) + 2 * nh * (d + e) * pairs
+        else:
+            r, t, qr = m["kv_rank"], m["rot_dim"], m["q_rank"]
+            w = m["mask"]["size"]
+            seen = pairs if tokens <= w else w * (w + 1) // 2 + (tokens - w) * w
+            flops += 2 * tokens * ((qr + r + t) * W + nh * (d + t) * qr + nh * d * r + nh * e * r + W * nh * e)
+            flops += 2 * nh * (2 * r + t) * seen
+    return flops, scan
+
+
+def graph_median_us(launch, sets):
+    """Microseconds per launch inside a captured graph of at least 16 launches over rotating tensors (a launch by
+    itself from the host costs more than small kernels run; inside a step they are nodes of such a graph)."""
+    import torch
+    n = max(sets, 16)
+    for i in range(n):
+        launch(i % sets)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(n):
+            launch(i % sets)
+    for _ in range(3):
+        graph.replay()
+    events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(15)]
+    torch.cuda.synchronize()
+    for a, b in events:
+        a.record()
+        graph.replay()
+        b.record()
+    torch.cuda.synchronize()
+    times = sorted(a.elapsed_time(b) * 1e3 / n for a, b in events)
+    return times[len(times) // 2]
+
+
+def zepilix_kernel_rows(pk, llama):
+    """Each kernel the design adds, alone, beside the like kernel of the closest existing path at the same sizes:
+    microseconds per launch inside a captured graph over rotating tensors, the share of the measured copy bandwidth
+    that the bytes it must move make, and for the recurrence its share of the FP32 pipes."""
+    import torch
+
+    from lyapunov_engine_b200 import ops
+    from lyapunov_engine_b200.engine.runtime import Workspace
+    from lyapunov_engine_b200.parts.rope import pair_rates
+
+    dev = "cuda:0"
+    cfg = zepilix_config(llama)
+    W, nh, nkv, hd, F = llama["hidden_size"], llama["num_attention_heads"], llama["num_key_value_heads"], llama["head_dim"], llama["intermediate_size"]
+    dm = cfg["layers"][0]["mixer"]
+    H, G, d, e = dm["heads"], dm["kv_heads"], dm["dim"], dm["vdim"]
+    r, t, page, s = ZEPILIX_LATENT, ZEPILIX_TURNED, BLOCK_SIZE, ZEPILIX_SIDE
+    rows = []
+
+    def row(kernel, like, tokens, nbytes, launch, sets, fp32_flops=0):
+        us = graph_median_us(launch, sets)
+        entry = {"kernel": kernel, "like": like, "tokens": tokens, "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1),
+                 "hbm_frac": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)}
+        if fp32_flops:
+            # 148 multiprocessors x 128 lanes x 2 flops at the highest clock (1,965 MHz): 74.4 TFLOP/s
+            entry["fp32_frac"] = round(fp32_flops / us / 1e6 / 74.4, 3)
+        rows.append(entry)
+
+    def sets_for(nbytes):
+        return max(2, min(64, (256 << 20) // max(nbytes, 1) + 1))
+
+    bf = torch.bfloat16
+    status = ops.new_status(dev)
+    ws = Workspace(torch.device(dev))
+    for T in (8, 2048):
+        # the two norms of one row, with the normed addend of the token's input; the Llama path's norm + residual
+        nbytes = T * W * (4 + 2 + 4 + 2 + 2) + 12 * W
+        n = sets_for(nbytes)
+        resid = [torch.randn(T, W, device=dev) for _ in range(n)]
+        addend = [torch.randn(T, W, device=dev).to(bf) for _ in range(n)]
+        o1 = [torch.empty(T, W, device=dev, dtype=bf) for _ in range(n)]
+        o2 = [torch.empty(T, W, device=dev, dtype=bf) for _ in range(n)]
+        w1, w2, wa = (torch.ones(W, device=dev) for _ in range(3))
+        row("two norms of one row + normed addend", "", T, nbytes,
+            lambda i: ops.rmsnorm_pair(o1[i], o2[i], resid[i], w1, w2, 1e-6, addend=addend[i], addend_weight=wa, addend_eps=1e-6), n)
+        row("rmsnorm + residual", "two norms of one row + normed addend", T, T * W * 12 + 4 * W,
+            lambda i: ops.rmsnorm(o1[i], resid[i], addend[i], w1, 1e-5), n)
+        # both sub-layers' outputs and the bias into the stream, with the copy the token's input reads
+        bias = torch.randn(W, device=dev)
+        row("sum of both sub-layers into the stream + copy", "", T, T * W * (8 + 2 + 2 + 2) + 4 * W,
+            lambda i: ops.residual_add(resid[i], addend[i], o2[i], bias, o1[i]), n)
+        # the gate of the token's input, and what a pass adds
+        z = torch.randn(T, s, device=dev).to(bf)
+        table = torch.randn(32000, 4 * s, device=dev).to(bf)
+        ids = torch.randint(0, 32000, (T,), dtype=torch.int32, device=dev)
+        gz = torch.empty(T, s, device=dev, dtype=bf)
+        row("gelu gate times the token's table row", "", T, T * s * 6, lambda i: ops.gate_rows(gz, z, table, s, ids, status), 1)
+        emb = torch.randn(32000, W, device=dev).to(bf)
+        vec = torch.randn(W, device=dev)
+        row("pass entry (embedding + vector into the stream)", "", T, T * W * 10, lambda i: ops.stream_entry(resid[i], emb, ids, vec, status), n)
+        row("embedding", "pass entry", T, T * W * 6, lambda i: ops.embed(resid[i], emb, ids, status), n)
+        del resid, addend, o1, o2
+        # the delta rule's chain: convolution with silu over q | k | v, the recurrence, the gated norm per head
+        C = 2 * G * d + H * e
+        width = C + H * e + 2 * H
+        width = (width + 7) // 8 * 8
+        reqs = T if T <= 64 else 1
+        q_lens = [T // reqs] * reqs
+        cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=dev)
+        treq = torch.tensor([b for b, m in enumerate(q_lens) for _ in range(0, m, ops.SHORT_CONV_TILE)], dtype=torch.int32, device=dev)
+        tq0 = torch.tensor([s0 for m in q_lens for s0 in range(0, m, ops.SHORT_CONV_TILE)], dtype=torch.int32, device=dev)
+        slots = torch.arange(reqs, dtype=torch.int32, device=dev)
+        proj = torch.randn(T, width, device=dev).to(bf)
+        conv = torch.empty(T, C, device=dev, dtype=bf)
+        taps_state = torch.zeros(reqs + 1, 3, C, device=dev)
+        taps = torch.randn(4, C, device=dev)
+        if T <= 64:
+            launch = lambda i: ops.short_conv_general(conv, proj[:, :C], taps, taps_state, slots, cu, None, None, reqs, add_input=False, silu=True)
+        else:
+            launch = lambda i: ops.short_conv_general(conv, proj[:, :C], taps, taps_state, slots, cu, treq, tq0, treq.numel(), add_input=False, silu=True)
+        row(f"convolution (4 taps) + silu over {C} channels", "short convolution, 4 taps (Sulepel, 2,048 channels)", T,
+            T * C * 4 + reqs * 3 * C * 8 + 16 * C, launch, 1)
+        state_sets = 4 if T <= 64 else 2
+        states = [torch.zeros(reqs + 1, H, e, d, device=dev) for _ in range(state_sets)]
+        o = torch.empty(T, H * e, device=dev)
+        a_log, dt_bias = torch.zeros(H, device=dev), torch.zeros(H, device=dev)
+        conv.normal_()
+        row(f"delta rule, {H} heads of {d} x {e}, {reqs} request(s)", "", T, reqs * 2 * 4 * H * d * e + T * (C * 2 + H * e * 4),
+            lambda i: ops.gated_delta_scan(o, conv, 0, G * d, 2 * G * d, proj, C + H * e, C + H * e + H, a_log, dt_bias, states[i],
+                                           slots, cu, reqs, H, G, d, e, 1e-6, d ** -0.5), state_sets, fp32_flops=6 * T * H * d * e)
+        gated = torch.empty(T, H * e, device=dev, dtype=bf)
+        wn = torch.ones(e, device=dev)
+        row("norm per head times silu gate", "", T, T * H * e * 8, lambda i: ops.head_norm_gate(gated, o, proj[:, C:C + H * e], wn, 1e-6, H, e), 1)
+        # cache writes
+        pages = (T + page - 1) // page + 1
+        btab = torch.arange(pages, dtype=torch.int32, device=dev).view(1, -1).contiguous()
+        req0 = torch.zeros(T, dtype=torch.int32, device=dev)
+        pos = torch.arange(T, dtype=torch.int32, device=dev)
+        qk = torch.randn(T, (nh + nkv) * hd, device=dev).to(bf)
+        kc = torch.zeros(pages + 1, nkv, page, hd, device=dev, dtype=bf)
+        vc = torch.zeros_like(kc)
+        rates = pair_rates(hd, 5e5).to(dev)
+        row("turn of pairs + norm + cache write (values are the keys)", "", T, T * ((nh + nkv) * hd * 4 + nkv * hd * 2),
+            lambda i: ops.rope_norm_store(qk, kc, vc, rates, pos, req0, btab, nh, nkv, hd, 0, hd, 1e-6, hd, page, True, True, status), 1)
+        qkv = torch.randn(T, (nh + 2 * nkv) * hd, device=dev).to(bf)
+        cos_sin = torch.randn(max(T, 16), hd, device=dev)
+        row("rotary + key/value cache write", "turn of pairs + norm + cache write", T, T * ((nh + nkv) * hd * 4 + nkv * hd * 4),
+            lambda i: ops.rope_kv_write(qkv, kc, vc, cos_sin, pos, req0, btab, nh, nkv, hd, page, True, status), 1)
+        qr = W * 3 // 8
+        down = torch.randn(T, qr + r + t, device=dev).to(bf)
+        lat = torch.zeros(pages + 1, 1, page, r + t, device=dev, dtype=bf)
+        wl, wq = torch.ones(r, device=dev), torch.ones(qr, device=dev)
+        cq = torch.empty(T, qr, device=dev, dtype=bf)
+        rates_l = pair_rates(t, 1e6).to(dev)
+        row("both latents' norms + turned key part + cache write", "", T, T * (qr + r + t) * 4,
+            lambda i: ops.latent_rope_store(down, qr, r, t, r + t, wl, 1e-6, rates_l, lat, pos, req0, btab, page, status, second=(0, qr, wq, cq)), 1)
+        lat2 = torch.zeros(pages + 1, 1, page, 128, device=dev, dtype=bf)
+        proj2 = torch.randn(T, 128 + 8, device=dev).to(bf)
+        wl2 = torch.ones(128, device=dev)
+        row("latent norm + cache write", "both latents' norms + turned key part + cache write", T, T * 128 * 4,
+            lambda i: ops.latent_norm_store(proj2, 0, 128, wl2, 1e-5, lat2, pos, req0, btab, page, status), 1)
+        # gated products with and without biases
+        x = torch.randn(T, W, device=dev).to(bf)
+        wgu = [torch.randn(2 * F, W, device=dev).to(bf) for _ in range(4)]
+        act = torch.empty(T, F, device=dev, dtype=bf)
+        b2 = torch.randn(2 * F, device=dev)
+        nbytes = 2 * (2 * F * W + T * W + T * F)
+        row("gate/up product, biases + SiLU", "", T, nbytes + 8 * F, lambda i: ops.gated_linear_bias(act, x, wgu[i], b2, ws, status), 4)
+        row("gate/up product, SiLU", "gate/up product, biases + SiLU", T, nbytes, lambda i: ops.gated_linear(act, x, wgu[i], ws, status), 4)
+        del wgu
+    ops.check_status(status)
+    return rows
+
+
+def run_zepilix(args):
+    """--only zepilix: decode (1 and 8 requests at --context) and prefill (2,048 tokens) of a Zepilix model beside the
+    Sulepel model (the closest existing design: latent attention, short convolutions, state rows per request) and the
+    Llama model of the same width, feed-forward size, heads, layer runs and vocabulary (random weights, bfloat16),
+    and the design's own kernels alone beside their likes."""
+    global BLOCK_SIZE
+    import torch
+
+    BLOCK_SIZE = args.page
+    pk = peaks()
+    context = args.context or CONTEXT
+    if args.profile_step:
+        # a few steps launch by launch (no captured graph) of a model of --layers layer runs (4 by default), for a profiler
+        llama = dict(SHAPES[args.shapes])
+        llama["num_hidden_layers"] = args.layers or 4
+        rig = make_rig(zepilix_config(llama), context, 8, args.page)
+        rig.runner.use_cuda_graphs = False
+        if args.profile_step == "decode":
+            ms, _, _ = rig.timed_decode(args.batch, 2, 2, context)
+        else:
+            ms = rig.timed_prefill(args.tokens or PREFILL_TOKENS, 1, 2)
+        print(json.dumps({"only": "zepilix", "profile_step": args.profile_step, "layers": llama["num_hidden_layers"], "ms": round(ms, 3)}))
+        return 0
+    out = {"only": "zepilix", "peaks": pk["source"], "context": context, "sizes": {}}
+    for name in ([args.shapes] if args.shapes != "1b" or args.layers else ["1b", "3b"]):
+        llama = dict(SHAPES[name])
+        if args.layers:
+            llama["num_hidden_layers"] = args.layers
+        res = {}
+        for label, cfg in (("zepilix", zepilix_config(llama)), ("sulepel", sulepel_config(llama)), ("llama", llama)):
+            rig = make_rig(cfg, context, 8, args.page)
+            for b in (1, 8):
+                rig.timed_decode(b, 3, 2, context - 200)
+                ms, graph_steps, _ = rig.timed_decode(b, 24, 6, context)
+                nbytes = {"zepilix": zepilix_decode_bytes, "sulepel": sulepel_decode_bytes, "llama": decode_bytes}[label](cfg, b, context - 12)
+                res[f"{label}_decode_b{b}_ms"] = round(ms, 4)
+                res[f"{label}_decode_b{b}_tokens_per_s"] = round(b * 1000.0 / ms, 1)
+                res[f"{label}_decode_b{b}_hbm_frac"] = round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+                res[f"{label}_decode_b{b}_graph_steps"] = graph_steps
+            ms = rig.timed_prefill(PREFILL_TOKENS, 3, 2)
+            if label == "zepilix":
+                flops, scan = zepilix_prefill_flops(cfg, PREFILL_TOKENS)
+                res["zepilix_prefill_fp32_recurrence_gflop"] = round(scan / 1e9, 2)
+            else:
+                flops = sulepel_prefill_flops(cfg, PREFILL_TOKENS) if label == "sulepel" else prefill_flops(cfg, PREFILL_TOKENS)
+            res[f"{label}_prefill_{PREFILL_TOKENS}_ms"] = round(ms, 3)
+            res[f"{label}_prefill_{PREFILL_TOKENS}_tokens_per_s"] = round(PREFILL_TOKENS * 1000.0 / ms, 1)
+            res[f"{label}_prefill_{PREFILL_TOKENS}_bf16_frac"] = round(flops / (ms * 1e-3) / 1e12 / pk["bf16_tflops"], 4)
+            rig.close()
+            del rig
+            torch.cuda.empty_cache()
+        out["sizes"][name] = res
+        for k, v in res.items():
+            print(f"{name}  {k} = {v}", file=sys.stderr)
+    rows = zepilix_kernel_rows(pk, dict(SHAPES["1b"]))
+    for r in rows:
+        print("  ".join(f"{k}={v}" for k, v in r.items() if v != ""), file=sys.stderr)
+    out["kernels"] = rows
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=1)
@@ -1302,13 +1613,13 @@ def main():
     p.add_argument("--warmup", type=int, default=16)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
-    p.add_argument("--only", choices=["decode", "prefill", "mixed", "serving", "kernels", "sulepel", "kaditar"], default=None,
+    p.add_argument("--only", choices=["decode", "prefill", "mixed", "serving", "kernels", "sulepel", "kaditar", "zepilix"], default=None,
                    help="run one kind of step and exit (for profilers and for further sizes); mixed = --batch decoding "
                         "requests beside one --tokens portion of a prompt in every step; serving = the reference's "
                         "serving benchmark (small model, prompts of 128 tokens, 32 generated: TTFT, ITL, tokens/s); "
                         "kernels = its kernel benchmark (RMSNorm and prefill attention over a grid of sizes); "
                         "sulepel = the Sulepel design beside Llama at equal sizes (decode, prefill, its kernels alone); "
-                        "kaditar = the same for the Kaditar design")
+                        "kaditar = the same for the Kaditar design; zepilix = the Zepilix design beside Sulepel and Llama")
     p.add_argument("--batch-sizes", nargs="+", type=int, default=[1, 4, 8, 16], help="with --only serving")
     p.add_argument("--shapes", choices=sorted(SHAPES), default="1b", help="with --only: layer sizes of Llama-3.2-1B, 3.2-3B or 3.1-8B")
     p.add_argument("--batch", type=int, default=8, help="batch of --only decode")
@@ -1322,7 +1633,7 @@ def main():
     p.add_argument("--without", choices=["norms", "qkv", "attention", "o", "gate_up", "down", "head"], default=None,
                    help="with --only decode (batches up to 16): time the step with this kind of kernel left out")
     p.add_argument("--profile-step", choices=["decode", "prefill"], default=None,
-                   help="with --only sulepel: run a few steps of that kind launch by launch (no captured graph) on a model of "
+                   help="with --only sulepel, kaditar or zepilix: run a few steps of that kind launch by launch (no captured graph) on a model of "
                         "--layers layers (4 by default) and exit; for profilers")
     p.add_argument("--points", choices=["all", "1b"], default="all",
                    help="all: also decode, prefill and the mixed step at the 3B and 8B shapes (context 8192) in `points`")
@@ -1340,6 +1651,8 @@ def main():
         return run_sulepel(args)
     if args.only == "kaditar" and args.impl == "ours":
         return run_kaditar(args)
+    if args.only == "zepilix" and args.impl == "ours":
+        return run_zepilix(args)
     if args.impl == "reference":
         return run_reference(args)
     return run_ours(args)
