@@ -8,11 +8,12 @@
 // head the entries (rot_col + 2i, rot_col + 2i + 1), 2i + 1 < rot, turn by the
 // angle position * rates[i]: (a, b) -> (a cos - b sin, b cos + a sin).  With
 // `unit` set the turned head is then divided by sqrt(mean(head^2) + eps) over
-// its first norm_dim entries (the entries behind them are padding and zero).  Queries are rewritten in place; keys go to the key
-// pool; the value pool receives the keys as projected (before turn and norm)
-// when `values_are_keys`, else nothing.  A warp takes a head, a lane up to
-// eight pairs of it.  Angle, sine, cosine, turn and norm are 32-bit; the
-// result is rounded once.
+// its first norm_dim entries (the entries behind them are padding and zero).
+// Queries are rewritten in place; keys go to the key pool; the value pool
+// receives the keys as projected (before turn and norm) when
+// `values_are_keys`, else nothing.  A warp takes a head, a lane up to eight
+// pairs of it; a token's sines and cosines are made once per block.  Angle,
+// sine, cosine, turn and norm are 32-bit; the result is rounded once.
 //
 // latent_rope_store_kernel.  Columns [col, col + rank) of a token's row are a
 // latent: normed with a weight over `rank`; the `rot` columns behind it are one
@@ -27,18 +28,51 @@ namespace {
 
 constexpr int RN_MAX_PAIRS = 8;      // pairs a lane holds: heads of up to 512 entries
 
+// Two neighbouring entries at once where the address allows it.
+template <typename T>
+__device__ __forceinline__ void load_pair(const T *p, bool together, float &u, float &v) {
+  if (together) {
+    if constexpr (sizeof(T) == 2) {
+      const uint32_t r = *reinterpret_cast<const uint32_t *>(p);
+      u = __uint_as_float(r << 16), v = __uint_as_float(r & 0xffff0000u);
+    } else {
+      const float2 r = *reinterpret_cast<const float2 *>(p);
+      u = r.x, v = r.y;
+    }
+  } else {
+    u = le::to_f32(p[0]), v = le::to_f32(p[1]);
+  }
+}
+template <typename T>
+__device__ __forceinline__ void store_pair(T *p, bool together, float u, float v) {
+  if (together) {
+    if constexpr (sizeof(T) == 2) {
+      *reinterpret_cast<__nv_bfloat162 *>(p) = __floats2bfloat162_rn(u, v);
+    } else {
+      *reinterpret_cast<float2 *>(p) = make_float2(u, v);
+    }
+  } else {
+    p[0] = le::from_f32<T>(u), p[1] = le::from_f32<T>(v);
+  }
+}
+
+// A block takes a token and `heads_per_block` of its heads (queries first, then keys), a warp one head at a time.  The
+// token's sines and cosines are made once per block, in shared memory.
 template <typename T>
 __global__ void __launch_bounds__(128)
 rope_norm_store_kernel(T *__restrict__ rows, int64_t row_stride, T *__restrict__ k_cache, T *__restrict__ v_cache,
                        const float *__restrict__ rates, const int32_t *__restrict__ positions,
                        const int32_t *__restrict__ request_of_token, const int32_t *__restrict__ block_table,
                        int max_blocks, int heads, int kv_heads, int head_dim, int rot_col, int rot, int unit, float eps,
-                       int norm_dim, int page_size, int num_pages, int write_kv, int values_are_keys, int *__restrict__ status) {
+                       int norm_dim, int page_size, int num_pages, int write_kv, int values_are_keys, int heads_per_block,
+                       int together, int *__restrict__ status) {
+  extern __shared__ float turn[];            // [rot / 2][2]: sine, cosine
   le::let_successor_start();
   le::wait_for_predecessor();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const float fpos = static_cast<float>(pos);
+  for (int i = threadIdx.x; i < (rot >> 1); i += blockDim.x) sincosf(fpos * rates[i], &turn[2 * i], &turn[2 * i + 1]);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   T *row = rows + static_cast<int64_t>(t) * row_stride;
   int page = 0;
@@ -47,10 +81,13 @@ rope_norm_store_kernel(T *__restrict__ rows, int64_t row_stride, T *__restrict__
     const int b = request_of_token[t];
     page = pos >= 0 ? block_table[static_cast<int64_t>(b) * max_blocks + pos / page_size] : -1;
     bad = page < 0 || page >= num_pages;
-    if (bad && threadIdx.x == 0) atomicOr(status, LE_STATUS_BAD_PAGE);
+    if (bad && threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, LE_STATUS_BAD_PAGE);
   }
+  __syncthreads();
   const int pairs = head_dim >> 1;
-  for (int h = warp; h < heads + (write_kv ? kv_heads : 0); h += warps) {
+  const int all = heads + (write_kv ? kv_heads : 0);
+  const int h_end = min(all, (static_cast<int>(blockIdx.y) + 1) * heads_per_block);
+  for (int h = blockIdx.y * heads_per_block + warp; h < h_end; h += warps) {
     T *x = row + static_cast<int64_t>(h) * head_dim;
     const bool is_key = h >= heads;
     if (is_key && bad) continue;
@@ -66,13 +103,12 @@ rope_norm_store_kernel(T *__restrict__ rows, int64_t row_stride, T *__restrict__
     for (int i = 0; i < RN_MAX_PAIRS; ++i) {
       const int p = lane + 32 * i;
       if (p < pairs) {
-        const T ra = x[2 * p], rb = x[2 * p + 1];
-        if (v_dst != nullptr) v_dst[2 * p] = ra, v_dst[2 * p + 1] = rb;
-        float u = le::to_f32(ra), v = le::to_f32(rb);
+        float u, v;
+        load_pair(x + 2 * p, together, u, v);
+        if (v_dst != nullptr) store_pair(v_dst + 2 * p, together, u, v);     // (as projected: the same bits)
         const int j = 2 * p - rot_col;
         if (j >= 0 && j + 1 < rot) {
-          float s, c;
-          sincosf(fpos * rates[j >> 1], &s, &c);
+          const float s = turn[j], c = turn[j + 1];
           const float nu = u * c - v * s, nv = v * c + u * s;
           u = nu, v = nv;
         }
@@ -86,7 +122,7 @@ rope_norm_store_kernel(T *__restrict__ rows, int64_t row_stride, T *__restrict__
 #pragma unroll
     for (int i = 0; i < RN_MAX_PAIRS; ++i) {
       const int p = lane + 32 * i;
-      if (p < pairs) dst[2 * p] = le::from_f32<T>(a[i] * inv), dst[2 * p + 1] = le::from_f32<T>(b[i] * inv);
+      if (p < pairs) store_pair(dst + 2 * p, together, a[i] * inv, b[i] * inv);
     }
   }
 }
@@ -104,29 +140,36 @@ latent_rope_store_kernel(const T *__restrict__ src, int64_t src_stride, int col,
   le::wait_for_predecessor();
   const int t = blockIdx.x;
   const T *row = src + static_cast<int64_t>(t) * src_stride;
+  // Everything is asked for before anything is waited for: the page, both latents' sums of squares.
+  int pos = 0, page = -1;
+  if (cache != nullptr) {
+    pos = positions[t];
+    const int b = request_of_token[t];
+    page = pos >= 0 ? block_table[static_cast<int64_t>(b) * max_blocks + pos / page_size] : -1;
+  }
+  const T *x = row + col;
+  float ss2 = 0.0f, ss = 0.0f;
   if (out2 != nullptr) {
-    float ss = 0.0f;
     for (int i = threadIdx.x; i < rank2; i += blockDim.x) {
       const float v = le::to_f32(row[col2 + i]);
+      ss2 = fmaf(v, v, ss2);
+    }
+  }
+  if (cache != nullptr) {
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) {
+      const float v = le::to_f32(x[i]);
       ss = fmaf(v, v, ss);
     }
-    ss = le::block_sum(ss, scratch);
-    const float inv = rsqrtf(ss / static_cast<float>(rank2) + eps);
+  }
+  if (out2 != nullptr) {
+    ss2 = le::block_sum(ss2, scratch);
+    const float inv = rsqrtf(ss2 / static_cast<float>(rank2) + eps);
     T *dst = out2 + static_cast<int64_t>(t) * out2_stride;
     for (int i = threadIdx.x; i < rank2; i += blockDim.x) dst[i] = le::from_f32<T>(le::to_f32(row[col2 + i]) * inv * weight2[i]);
   }
   if (cache == nullptr) return;
-  const int pos = positions[t];
-  const int b = request_of_token[t];
-  const int page = pos >= 0 ? block_table[static_cast<int64_t>(b) * max_blocks + pos / page_size] : -1;
   const bool bad = page < 0 || page >= num_pages;
   if (bad && threadIdx.x == 0) atomicOr(status, LE_STATUS_BAD_PAGE);
-  const T *x = row + col;
-  float ss = 0.0f;
-  for (int i = threadIdx.x; i < rank; i += blockDim.x) {
-    const float v = le::to_f32(x[i]);
-    ss = fmaf(v, v, ss);
-  }
   ss = le::block_sum(ss, scratch);
   if (bad) return;
   const float inv = rsqrtf(ss / static_cast<float>(rank) + eps);
@@ -164,12 +207,20 @@ LE_API int le_rope_norm_store(void *rows, int64_t row_stride, int dtype, void *k
     return le::invalid("le_rope_norm_store: heads of %d entries (even, at most %d)", head_dim, 64 * RN_MAX_PAIRS);
   if (rot < 0 || rot % 2 || rot_col < 0 || rot_col % 2 || rot_col + rot > head_dim)
     return le::invalid("le_rope_norm_store: %d turned entries from column %d of a head of %d", rot, rot_col, head_dim);
+  const int all = heads + (write_kv ? kv_heads : 0);
+  const int per_block = num_tokens >= 512 ? 16 : 4;       // few tokens: more blocks; many: the sines serve more heads
+  const dim3 grid(num_tokens, (all + per_block - 1) / per_block);
+  if (grid.y > 65535) return le::invalid("le_rope_norm_store: %d heads are too many for one launch", all);
+  const size_t elem = dtype == LE_BF16 ? 2 : 4;
+  const auto pairs_aligned = [&](const void *p) { return reinterpret_cast<uintptr_t>(p) % (2 * elem) == 0; };
+  const int together = pairs_aligned(rows) && row_stride % 2 == 0 && pairs_aligned(k_cache) && pairs_aligned(v_cache);
+  const size_t smem = sizeof(float) * (rot > 0 ? rot : 2);
   LE_DISPATCH_DTYPE(dtype, T,
-                    return le::launch_chained(rope_norm_store_kernel<T>, dim3(num_tokens), dim3(128), 0, stream,
+                    return le::launch_chained(rope_norm_store_kernel<T>, grid, dim3(128), smem, stream,
                                               static_cast<T *>(rows), row_stride, static_cast<T *>(k_cache),
                                               static_cast<T *>(v_cache), rates, positions, request_of_token, block_table,
                                               max_blocks, heads, kv_heads, head_dim, rot_col, rot, unit, eps, norm_dim,
-                                              page_size, num_pages, write_kv, values_are_keys, status));
+                                              page_size, num_pages, write_kv, values_are_keys, per_block, together, status));
 }
 
 // cache: [pages, 1, page, padded] or null (nothing is stored); out2 null: no second latent.

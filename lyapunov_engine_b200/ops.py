@@ -84,9 +84,10 @@ _CORE_SIGNATURES = {
                               c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "le_glu_bias": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p],
     "le_gated_delta_lanes": [c_int],
+    "le_gated_delta_scratch": [c_int, c_int],
     "le_gated_delta_scan": [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_int64, c_int, c_int, c_int,
-                            c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                            c_float, c_float, c_void_p],
+                            c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                            c_float, c_float, c_void_p, c_void_p],
     "le_head_norm_gate": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p, c_float, c_int, c_int,
                           c_int, c_void_p],
     "le_rope_norm_store": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
@@ -1214,8 +1215,13 @@ def short_conv_general(out, h, w_taps, state, state_slots, cu_q, tile_request, t
 GATED_DELTA_MAX_DIM = 1024
 
 
+def gated_delta_scratch_width(heads: int, kv_heads: int) -> int:
+    """Floats per token of the scratch rows that ``gated_delta_scan`` fills (inverse lengths, k . q, decay, step size)."""
+    return 4 * int(kv_heads) + 2 * int(heads)
+
+
 def gated_delta_scan(out, qkv, q_col, k_col, v_col, proj, b_col, a_col, a_log, dt_bias, state, state_slots, cu_q,
-                     num_requests, heads, kv_heads, dim, vdim, unit_eps, q_scale) -> None:
+                     num_requests, heads, kv_heads, dim, vdim, unit_eps, q_scale, scratch=None) -> None:
     """The gated delta rule over the step's tokens, request by request, from
     each request's state row and back into it.  ``out``: float32 [T, heads *
     vdim].  ``qkv``: rows with queries and keys [kv_heads, dim] at columns
@@ -1223,16 +1229,22 @@ def gated_delta_scan(out, qkv, q_col, k_col, v_col, proj, b_col, a_col, a_log, d
     keys are made unit vectors here (x / sqrt(sum x^2 + unit_eps)), queries
     times ``q_scale``.  ``proj``: rows with one number per head at ``b_col``
     (step size = its sigmoid) and ``a_col`` (decay = exp(-exp(a_log) *
-    softplus(a + dt_bias))).  ``state``: float32 [rows, heads, vdim, dim]."""
+    softplus(a + dt_bias))).  ``state``: float32 [rows, heads, vdim, dim].
+    ``scratch``: float32 [T, gated_delta_scratch_width()], made here if None."""
     _need_cuda(out, qkv, proj, a_log, dt_bias, state, state_slots, cu_q)
+    T = out.shape[0]
     assert out.dtype == torch.float32 and out.stride(1) == 1 and qkv.stride(1) == 1 and proj.stride(1) == 1
     assert qkv.dtype == proj.dtype and a_log.dtype == torch.float32 and dt_bias.dtype == torch.float32
-    assert a_log.numel() == heads and dt_bias.numel() == heads
+    assert a_log.numel() == heads and dt_bias.numel() == heads and qkv.shape[0] == T and proj.shape[0] == T
     assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, vdim, dim)
+    width = gated_delta_scratch_width(heads, kv_heads)
+    if scratch is None:
+        scratch = torch.empty((max(T, 1), width), dtype=torch.float32, device=out.device)
+    assert scratch.dtype == torch.float32 and scratch.is_contiguous() and scratch.shape[0] >= T and scratch.shape[1] == width
     _check(core().le_gated_delta_scan(_ptr(out), out.stride(0), _ptr(qkv), qkv.stride(0), q_col, k_col, v_col, _ptr(proj),
                                       proj.stride(0), b_col, a_col, dtype_code(qkv.dtype), _ptr(a_log), _ptr(dt_bias),
-                                      _ptr(state), state.shape[0], _ptr(state_slots), _ptr(cu_q), num_requests, heads,
-                                      kv_heads, dim, vdim, float(unit_eps), float(q_scale), _stream()),
+                                      _ptr(state), state.shape[0], _ptr(state_slots), _ptr(cu_q), num_requests, T, heads,
+                                      kv_heads, dim, vdim, float(unit_eps), float(q_scale), _ptr(scratch), _stream()),
            "le_gated_delta_scan")
 
 

@@ -109,9 +109,10 @@ class GatedDeltaMixer(Mixer):
             ops.short_conv_general(conv, proj[:, :self.channels], self.w_taps, taps_state, ctx.state_slots, ctx.cu_q,
                                    tile_request, tile_q0, num_tiles, add_input=False, silu=True)
         o = ws.get("delta_out", (T, H * e), torch.float32)
+        scratch = ws.get("delta_numbers", (T, ops.gated_delta_scratch_width(H, G)), torch.float32)
         ops.gated_delta_scan(o, conv, self.q_col, self.k_col, self.v_col, proj, self.beta_col, self.decay_col, self.a_log,
                              self.dt_bias, cache.state, ctx.state_slots, ctx.cu_q, ctx.num_requests, H, G, d, e, UNIT_EPS,
-                             d ** -0.5)
+                             d ** -0.5, scratch=scratch)
         gated = ws.get("delta_gated", (T, H * e), rt.dtype)
         ops.head_norm_gate(gated, o, proj[:, self.gate_col:self.gate_col + H * e], self.norm_weight, self.norm_eps, H, e)
         return ops.linear_for_residual(gated, self.w_o, ws, "mixer_out", ctx.status)
