@@ -127,6 +127,120 @@ rope_norm_store_kernel(T *__restrict__ rows, int64_t row_stride, T *__restrict__
   }
 }
 
+// 16 bytes of a head at once, as floats and back.
+template <typename T>
+struct Piece;
+template <>
+struct Piece<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void open(const uint4 &r, float *d) {
+    d[0] = __uint_as_float(r.x << 16), d[1] = __uint_as_float(r.x & 0xffff0000u);
+    d[2] = __uint_as_float(r.y << 16), d[3] = __uint_as_float(r.y & 0xffff0000u);
+    d[4] = __uint_as_float(r.z << 16), d[5] = __uint_as_float(r.z & 0xffff0000u);
+    d[6] = __uint_as_float(r.w << 16), d[7] = __uint_as_float(r.w & 0xffff0000u);
+  }
+  static __device__ __forceinline__ uint4 close(const float *d, float f) {
+    uint4 r;
+    __nv_bfloat162 *o = reinterpret_cast<__nv_bfloat162 *>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] = __floats2bfloat162_rn(d[2 * i] * f, d[2 * i + 1] * f);
+    return r;
+  }
+};
+template <>
+struct Piece<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void open(const uint4 &r, float *d) {
+    d[0] = __uint_as_float(r.x), d[1] = __uint_as_float(r.y), d[2] = __uint_as_float(r.z), d[3] = __uint_as_float(r.w);
+  }
+  static __device__ __forceinline__ uint4 close(const float *d, float f) {
+    return make_uint4(__float_as_uint(d[0] * f), __float_as_uint(d[1] * f), __float_as_uint(d[2] * f), __float_as_uint(d[3] * f));
+  }
+};
+
+// The same in 16-byte pieces (heads that are whole pieces, rows and pools that start on 16 bytes): a head belongs to
+// `lph` neighbouring lanes (a power of two), a lane holds every lph-th piece of it, so a warp takes 32 / lph heads at
+// once and the sum of squares meets over lph lanes.
+template <typename T>
+__global__ void __launch_bounds__(128)
+rope_norm_store_pieces_kernel(T *__restrict__ rows, int64_t row_stride, T *__restrict__ k_cache, T *__restrict__ v_cache,
+                              const float *__restrict__ rates, const int32_t *__restrict__ positions,
+                              const int32_t *__restrict__ request_of_token, const int32_t *__restrict__ block_table,
+                              int max_blocks, int heads, int kv_heads, int head_dim, int rot_col, int rot, int unit, float eps,
+                              int norm_dim, int page_size, int num_pages, int write_kv, int values_are_keys,
+                              int heads_per_block, int lph, int *__restrict__ status) {
+  constexpr int N = Piece<T>::N;
+  constexpr int HELD = 2 * RN_MAX_PAIRS / N;          // pieces a lane holds at most
+  extern __shared__ float turn[];                     // [rot / 2][2]: sine, cosine
+  le::let_successor_start();
+  le::wait_for_predecessor();
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const float fpos = static_cast<float>(pos);
+  for (int i = threadIdx.x; i < (rot >> 1); i += blockDim.x) sincosf(fpos * rates[i], &turn[2 * i], &turn[2 * i + 1]);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  T *row = rows + static_cast<int64_t>(t) * row_stride;
+  int page = 0;
+  bool bad = false;
+  if (write_kv) {
+    const int b = request_of_token[t];
+    page = pos >= 0 ? block_table[static_cast<int64_t>(b) * max_blocks + pos / page_size] : -1;
+    bad = page < 0 || page >= num_pages;
+    if (bad && threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, LE_STATUS_BAD_PAGE);
+  }
+  __syncthreads();
+  const int at_once = 32 / lph, sub = lane % lph, mine = lane / lph;
+  const int pieces = head_dim / N;
+  const int all = heads + (write_kv ? kv_heads : 0);
+  const int h_end = min(all, (static_cast<int>(blockIdx.y) + 1) * heads_per_block);
+  for (int h0 = blockIdx.y * heads_per_block + warp * at_once; h0 < h_end; h0 += warps * at_once) {
+    const int h = h0 + mine;
+    const bool is_key = h >= heads;
+    const bool live = h < h_end && !(is_key && bad);
+    T *x = row + static_cast<int64_t>(h) * head_dim;
+    T *k_dst = nullptr, *v_dst = nullptr;
+    if (live && is_key) {
+      const int64_t at = ((static_cast<int64_t>(page) * kv_heads + (h - heads)) * page_size + pos % page_size) * head_dim;
+      k_dst = k_cache + at;
+      v_dst = values_are_keys ? v_cache + at : nullptr;
+    }
+    float val[HELD][N];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < HELD; ++i) {
+      const int c = sub + i * lph;
+      if (live && c < pieces) {
+        const uint4 raw = *reinterpret_cast<const uint4 *>(x + c * N);
+        if (v_dst != nullptr) *reinterpret_cast<uint4 *>(v_dst + c * N) = raw;     // (as projected: the same bits)
+        Piece<T>::open(raw, val[i]);
+#pragma unroll
+        for (int e = 0; e < N; e += 2) {
+          const int j = c * N + e - rot_col;
+          float u = val[i][e], v = val[i][e + 1];
+          if (j >= 0 && j + 1 < rot) {
+            const float sn = turn[j], cs = turn[j + 1];
+            const float nu = u * cs - v * sn, nv = v * cs + u * sn;
+            u = nu, v = nv;
+          }
+          val[i][e] = u, val[i][e + 1] = v;
+          ss = fmaf(u, u, fmaf(v, v, ss));
+        }
+      }
+    }
+    float inv = 1.0f;
+    if (unit) {
+      for (int o = 1; o < lph; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      inv = rsqrtf(ss / static_cast<float>(norm_dim) + eps);
+    }
+    T *dst = is_key ? k_dst : x;
+#pragma unroll
+    for (int i = 0; i < HELD; ++i) {
+      const int c = sub + i * lph;
+      if (live && c < pieces) *reinterpret_cast<uint4 *>(dst + c * N) = Piece<T>::close(val[i], inv);
+    }
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 latent_rope_store_kernel(const T *__restrict__ src, int64_t src_stride, int col, int rank, int rot, int padded,
@@ -215,6 +329,18 @@ LE_API int le_rope_norm_store(void *rows, int64_t row_stride, int dtype, void *k
   const auto pairs_aligned = [&](const void *p) { return reinterpret_cast<uintptr_t>(p) % (2 * elem) == 0; };
   const int together = pairs_aligned(rows) && row_stride % 2 == 0 && pairs_aligned(k_cache) && pairs_aligned(v_cache);
   const size_t smem = sizeof(float) * (rot > 0 ? rot : 2);
+  const int per_piece = static_cast<int>(16 / elem);
+  const auto on16 = [](const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  if (head_dim % per_piece == 0 && row_stride % per_piece == 0 && on16(rows) && on16(k_cache) && on16(v_cache)) {
+    int lph = 1;
+    while (lph < 32 && lph * per_piece < head_dim) lph <<= 1;
+    LE_DISPATCH_DTYPE(dtype, T,
+                      return le::launch_chained(rope_norm_store_pieces_kernel<T>, grid, dim3(128), smem, stream,
+                                                static_cast<T *>(rows), row_stride, static_cast<T *>(k_cache),
+                                                static_cast<T *>(v_cache), rates, positions, request_of_token, block_table,
+                                                max_blocks, heads, kv_heads, head_dim, rot_col, rot, unit, eps, norm_dim,
+                                                page_size, num_pages, write_kv, values_are_keys, per_block, lph, status));
+  }
   LE_DISPATCH_DTYPE(dtype, T,
                     return le::launch_chained(rope_norm_store_kernel<T>, grid, dim3(128), smem, stream,
                                               static_cast<T *>(rows), row_stride, static_cast<T *>(k_cache),
