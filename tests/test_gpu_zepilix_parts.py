@@ -85,7 +85,7 @@ def run_delta(seqs, cuts, slots_of, state_rows, H, G, d, e, a_log, dt_bias, dtyp
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,d,e", [(2, 1, 32, 32), (4, 2, 16, 24), (3, 3, 20, 12), (1, 1, 64, 100), (2, 1, 128, 64),
-                                     (2, 2, 48, 16), (1, 1, 1, 1), (2, 1, 256, 40), (1, 1, 200, 130)])
+                                     (2, 2, 48, 16), (1, 1, 1, 1), (2, 1, 256, 40), (1, 1, 200, 130), (1, 1, 320, 8), (1, 1, 520, 4)])
 def test_delta_rule_under_every_cut(H, G, d, e, dtype):
     """Three requests in cuts of unequal sizes, down to one token and across
     the kernel's tiles of tokens, on state rows that earlier requests left
