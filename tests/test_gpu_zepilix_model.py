@@ -352,6 +352,56 @@ def test_the_stream_after_every_layer_run(models):
         torch.testing.assert_close(got, ref.float(), atol=2e-4, rtol=2e-4)
 
 
+def draw_config(rng):
+    """A configuration with every size, the order of the layers and the loop drawn at random."""
+    def mlp():
+        return 0 if rng.random() < 0.15 else rng.choice([192, 256, 328, 448, 520, 1000])
+
+    def a_delta():
+        heads = rng.choice([1, 2, 4, 8])
+        return delta(heads, rng.choice([g for g in (1, 2, 4, 8) if heads % g == 0]), rng.choice([16, 32, 48, 64, 96, 128]),
+                     rng.choice([16, 32, 64, 80, 128]), rng.choice([2, 3, 4]), mlp())
+
+    def an_attention():
+        heads, dim = rng.choice([2, 4, 6, 8]), rng.choice([32, 64, 96, 128])
+        return attn(heads, rng.choice([g for g in (1, 2, 3, 4, 8) if heads % g == 0]), dim, rng.choice([dim, dim // 2, 16, 8]),
+                    rng.choice([1e4, 5e4, 5e5, 1e6]), rng.uniform(0.1, 0.3), mlp())
+
+    def a_latent():
+        return latent(rng.choice([2, 4, 5, 8]), rng.choice([32, 64, 128]), rng.choice([8, 16, 32, 64]), rng.choice([32, 64, 80, 128]),
+                      rng.choice([32, 48, 64, 96, 128, 160]), rng.choice([48, 80, 96, 128]),
+                      rng.choice([0, 17, 40, 64, 100, 150]), rng.choice([1e4, 1e6]), rng.uniform(0.08, 0.2), mlp())
+
+    n = rng.choice([3, 4, 5])
+    kinds = [a_delta, an_attention, a_latent] + [rng.choice([a_delta, an_attention, a_latent]) for _ in range(n - 3)]
+    rng.shuffle(kinds)
+    cfg = {"architecture": "Zepilix", "vocab": rng.choice([300, 512, 777, 1000]), "width": rng.choice([128, 192, 256, 320, 384]),
+           "norm": {"eps": rng.choice([1e-5, 1e-6])}, "layers": [kind() for kind in kinds]}
+    if rng.random() < 0.85:
+        cfg["token_side"] = {"dim": rng.choice([8, 16, 24, 32])}
+    if rng.random() < 0.8:
+        start = rng.randrange(0, n)
+        cfg["loop"] = {"start": start, "stop": rng.randrange(start + 1, n + 1), "times": rng.choice([2, 2, 3])}
+    return cfg
+
+
+@pytest.mark.parametrize("seed", [21, 22, 23])
+def test_configurations_drawn_at_random(seed, tmp_path_factory, tmp_path):
+    """Sizes, layer order, loop and page size drawn at random: whole prompts,
+    portions and a mixed batch on a pool that just holds the peak, both types."""
+    import random
+    rng = random.Random(seed)
+    cfg, page = draw_config(rng), rng.choice([16, 32, 64])
+    m = make_model(tmp_path_factory, f"drawn{seed}", cfg, page, pz.random_weights(cfg, seed=seed), (150, 70, 260, 33),
+                   (120, 64, 200, 2))
+    for dtype in ("float32", "bfloat16"):
+        check(m, ru.whole_trace(m["requests"]), dtype, tmp_path / f"w{dtype}", what=f"drawn {seed} {dtype} whole")
+        check(m, ru.portions_trace(m["requests"]), dtype, tmp_path / f"p{dtype}", what=f"drawn {seed} {dtype} portions")
+        trace = ru.mixed_trace(m["requests"], m["prompt_lens"], chunk=16, max_live=4, seed=5)
+        check(m, trace, dtype, tmp_path / f"m{dtype}", pool=ru.peak_pool_tokens(trace, page), what=f"drawn {seed} {dtype} mixed",
+              extra=("--max-num-seqs", "4"))
+
+
 def test_command_line_generates_from_random_weights(tmp_path):
     """`generate --random-weights` builds a Zepilix model from a config.json alone."""
     import subprocess
