@@ -47,7 +47,7 @@ CORE_KERNEL_SOURCES = ["kernels/elementwise.cu", "kernels/norm.cu", "kernels/rop
                        "kernels/gemm_f32.cu", "kernels/sampling.cu", "kernels/gemm_skinny.cu", "kernels/gemm_tc.cu",
                        "kernels/short_conv.cu", "kernels/kv_store.cu", "kernels/gemm_heads.cu", "kernels/streams.cu",
                        "kernels/rope_pairs.cu", "kernels/moe.cu", "kernels/delta_rule.cu", "kernels/rope_norm.cu",
-                       "kernels/residual.cu"]
+                       "kernels/residual.cu", "kernels/state_space.cu", "kernels/mlstm.cu", "kernels/rope_qknorm.cu"]
 ATTENTION_SOURCES = ["kernels/attention_generic.cu", "kernels/attention_mma.cu", "kernels/attention_tc.cu"]
 
 _lock = threading.Lock()

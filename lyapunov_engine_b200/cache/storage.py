@@ -48,7 +48,7 @@ class DeviceCache:
         self.num_blocks = int(num_blocks)
         self.max_num_seqs = int(max_num_seqs)
         groups = [host.CacheGroupSpec(block_size=self.block_size, window=int(g.window or 0), num_blocks=self.num_blocks,
-                                      chunk=int(g.chunk or 0)) for g in model.groups]
+                                      chunk=int(g.chunk or 0), keep_first=int(g.keep_first or 0)) for g in model.groups]
         self.manager = host.BlockSpaceManager(groups, self.max_num_seqs)
         self.streams: list[list[KVStream]] = []
         for gi, g in enumerate(model.groups):

@@ -60,14 +60,16 @@ PYBIND11_MODULE(_host, m) {
       .def("get_error", &Sequence::get_error);
 
   py::class_<CacheGroupSpec>(m, "CacheGroupSpec")
-      .def(py::init([](int block_size, int window, int num_blocks, int chunk) {
-             return CacheGroupSpec{block_size, window, num_blocks, chunk};
+      .def(py::init([](int block_size, int window, int num_blocks, int chunk, int keep_first) {
+             return CacheGroupSpec{block_size, window, num_blocks, chunk, keep_first};
            }),
-           py::arg("block_size") = 16, py::arg("window") = 0, py::arg("num_blocks") = 0, py::arg("chunk") = 0)
+           py::arg("block_size") = 16, py::arg("window") = 0, py::arg("num_blocks") = 0, py::arg("chunk") = 0,
+           py::arg("keep_first") = 0)
       .def_readwrite("block_size", &CacheGroupSpec::block_size)
       .def_readwrite("window", &CacheGroupSpec::window)
       .def_readwrite("num_blocks", &CacheGroupSpec::num_blocks)
-      .def_readwrite("chunk", &CacheGroupSpec::chunk);
+      .def_readwrite("chunk", &CacheGroupSpec::chunk)
+      .def_readwrite("keep_first", &CacheGroupSpec::keep_first);
 
   py::class_<BlockSpaceManager, std::shared_ptr<BlockSpaceManager>>(m, "BlockSpaceManager")
       .def(py::init<int, int, bool>(), py::arg("num_blocks"), py::arg("block_size") = 16,

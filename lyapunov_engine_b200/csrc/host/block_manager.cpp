@@ -17,6 +17,7 @@ BlockSpaceManager::BlockSpaceManager(std::vector<CacheGroupSpec> groups, int num
     if (g.window < 0) throw std::invalid_argument("BlockSpaceManager: window must be >= 0");
     if (g.chunk < 0) throw std::invalid_argument("BlockSpaceManager: chunk must be >= 0");
     if (g.window > 0 && g.chunk > 0) throw std::invalid_argument("BlockSpaceManager: a group has a window or chunks, not both");
+    if (g.keep_first < 0) throw std::invalid_argument("BlockSpaceManager: keep_first must be >= 0");
   }
   if (num_state_slots_ < 0) throw std::invalid_argument("BlockSpaceManager: num_state_slots must be >= 0");
   reset();
@@ -107,7 +108,9 @@ int BlockSpaceManager::release_passed(const SequencePtr &seq) {
     const int64_t first_needed = window > 0 ? computed - window + 1 : computed / chunk * chunk;
     if (first_needed <= 0) continue;
     const int64_t dead_pages = first_needed / groups_[g].block_size;
-    for (int64_t i = 0; i < dead_pages && i < static_cast<int64_t>(tables[g].size()); ++i) {
+    // pages that hold any of the first keep_first keys stay: every later query reads them
+    const int64_t kept_pages = (static_cast<int64_t>(groups_[g].keep_first) + groups_[g].block_size - 1) / groups_[g].block_size;
+    for (int64_t i = kept_pages; i < dead_pages && i < static_cast<int64_t>(tables[g].size()); ++i) {
       if (tables[g][i] >= 0) {
         release_page(static_cast<int>(g), tables[g][i]);
         tables[g][i] = -1;

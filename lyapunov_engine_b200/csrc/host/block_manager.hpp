@@ -9,7 +9,8 @@
 //   * cache groups: layers with different needs (all keys, or a window of
 //     them) have pools and block tables of their own;
 //   * pages that a window has passed (or that lie before the chunk the next
-//     query stands in) are given back while the request lives;
+//     query stands in) are given back while the request lives, except those
+//     that hold first keys every query keeps seeing (keep_first);
 //   * one arithmetic for prompts, portions and decoded tokens: grow(seq, n)
 //     makes room for the first n tokens; it changes nothing when it fails;
 //   * slots for per-request state of fixed size, taken with the first page
@@ -33,6 +34,7 @@ struct CacheGroupSpec {
   int window{0};      // 0: every key is kept; w > 0: a query at p reads keys p-w+1 .. p
   int num_blocks{0};  // pages of this group's pool
   int chunk{0};       // c > 0: a query at p reads keys floor(p / c) * c .. p (chunks counted from position 0)
+  int keep_first{0};  // n > 0 (with a window): the keys at positions 0 .. n-1 stay visible to every later query
 };
 
 class BlockSpaceManager {

@@ -5,7 +5,10 @@
 // of that request (all of them, a sliding window, or its own chunk) through
 // its block table, whether the step brings a whole prompt, a portion of two
 // tokens or one decoded token.  Scores are (q . k) * scale, times one number
-// per query head where `head_scale` is given.
+// per query head where `head_scale` is given; with `softcap` c > 0 a score s
+// becomes c * tanh(s / c).  With `keep_first` n > 0 the keys at positions
+// below n stay visible behind a window (le::key_visible): their tiles are
+// visited before the window's.
 //
 // One block per (tile of 16 query tokens of one request, query head).  Keys
 // are visited in tiles of 32 from position 0 (or the window's start) with a
@@ -47,7 +50,7 @@ attention_generic_kernel(T *__restrict__ out, int64_t out_stride, const T *__res
                          const int32_t *__restrict__ ctx_before, const int32_t *__restrict__ tile_request,
                          const int32_t *__restrict__ tile_q0, int num_heads, int num_kv_heads, int page_size,
                          int num_pages, int reach, float scale, const float *__restrict__ head_scale,
-                         int *__restrict__ status) {
+                         int keep_first, float softcap, int *__restrict__ status) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   GenericSmem &sm = *reinterpret_cast<GenericSmem *>(smem_raw);
 
@@ -78,14 +81,19 @@ attention_generic_kernel(T *__restrict__ out, int64_t out_stride, const T *__res
   for (int j = 0; j < HD / 8; ++j) acc[j] = 0.0f;
 
   const int k_begin = le::first_visible_key(p0, reach) / KT * KT;
+  // tiles of first keys that the window's tiles do not hold
+  const int keep_tiles = keep_first > 0 ? min((keep_first + KT - 1) / KT, k_begin / KT) : 0;
+  const int window_tiles = p_last >= k_begin ? (p_last - k_begin) / KT + 1 : 0;
 
-  for (int k0 = k_begin; k0 <= p_last; k0 += KT) {
+  for (int it = 0; it < keep_tiles + window_tiles; ++it) {
+    const bool kept_tile = it < keep_tiles;
+    const int k0 = kept_tile ? it * KT : k_begin + (it - keep_tiles) * KT;
     __syncthreads();
     // keys and values of this tile, one key row per group of 4 threads
     {
       const int kk = tid / 4, part = tid % 4;
       const int pos = k0 + kk;
-      const bool live = pos <= p_last;
+      const bool live = pos <= p_last && (!kept_tile || pos < keep_first);
       int page = 0;
       if (live) {
         page = table[pos / page_size];
@@ -114,8 +122,10 @@ attention_generic_kernel(T *__restrict__ out, int64_t out_stride, const T *__res
       float dot = 0.0f;
 #pragma unroll 8
       for (int d = 0; d < HD; ++d) dot = fmaf(sm.q[row][d], sm.k[kk][d], dot);
-      const bool seen = row < rows && pos <= p_row && pos >= lo_row;
-      s[c] = seen ? dot * scale : -INFINITY;
+      const bool seen = row < rows && le::key_visible(pos, p_row, lo_row, keep_first);
+      float score = dot * scale;
+      if (softcap > 0.0f) score = softcap * tanhf(score / softcap);
+      s[c] = seen ? score : -INFINITY;
       tile_max = fmaxf(tile_max, s[c]);
     }
 #pragma unroll
@@ -163,13 +173,14 @@ LE_API const char *le_last_error() { return le::error_buffer(); }
 // out: [T, num_heads * HD] with row stride out_stride; q: rows of stride
 // q_stride holding num_heads * HD query values; caches [pages, kv_heads,
 // page, HD].  tile_request / tile_q0 list the tiles of 16 query tokens.
-// `reach`: see le::first_visible_key; `head_scale`: num_heads floats or null.
+// `reach`: see le::first_visible_key; `head_scale`: num_heads floats or null; `keep_first`: see le::key_visible;
+// `softcap`: 0 for none.
 LE_API int le_attention_generic(void *out, int64_t out_stride, const void *q, int64_t q_stride, const void *k_cache,
                                 const void *v_cache, int dtype, const int32_t *block_table, int max_blocks,
                                 const int32_t *cu_q, const int32_t *ctx_before, const int32_t *tile_request,
                                 const int32_t *tile_q0, int num_tiles, int num_heads, int num_kv_heads, int page_size,
-                                int num_pages, int reach, float scale, const float *head_scale, int *status,
-                                cudaStream_t stream) {
+                                int num_pages, int reach, float scale, const float *head_scale, int keep_first,
+                                float softcap, int *status, cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
   if (num_kv_heads <= 0 || num_heads % num_kv_heads) return le::invalid("le_attention_generic: %d heads do not divide into %d groups", num_heads, num_kv_heads);
   if (num_heads > 65535) return le::invalid("le_attention_generic: too many heads for one launch");
@@ -186,7 +197,7 @@ LE_API int le_attention_generic(void *out, int64_t out_stride, const void *q, in
                                             static_cast<const T *>(k_cache), static_cast<const T *>(v_cache),          \
                                             block_table, max_blocks, cu_q, ctx_before, tile_request, tile_q0,          \
                                             num_heads, num_kv_heads, page_size, num_pages, reach, scale, head_scale,   \
-                                            status);                                                                   \
+                                            keep_first, softcap, status);                                                                \
   } while (0)
   if (dtype == LE_F32) LE_GO(float);
   else if (dtype == LE_BF16) LE_GO(__nv_bfloat16);

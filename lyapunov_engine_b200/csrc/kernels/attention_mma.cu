@@ -236,7 +236,7 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
                          const int32_t *__restrict__ ctx_before, const int32_t *__restrict__ tile_request,
                          const int32_t *__restrict__ tile_q0, int num_heads, int num_kv_heads, int page_size,
                          int page_shift, int num_pages, int reach, float scale, const float *__restrict__ head_scale,
-                         int *__restrict__ status) {
+                         int keep_first, float softcap, int *__restrict__ status) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   bf16 *q_tile = reinterpret_cast<bf16 *>(smem_raw);
   bf16 *k_tiles = q_tile + PF_BM * HD;
@@ -265,10 +265,14 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
   }
   const int k_begin = le::first_visible_key(p0, reach) / BN * BN;
   const int k_end = p_last + 1;
-  const int num_tiles = (k_end - k_begin + BN - 1) / BN;
+  // tiles of first keys that stay visible behind the window and that the window's tiles do not hold come first
+  const int keep_tiles = keep_first > 0 ? min((keep_first + BN - 1) / BN, k_begin / BN) : 0;
+  const int num_tiles = keep_tiles + (k_end - k_begin + BN - 1) / BN;
+  auto tile_k0 = [&](int it) { return it < keep_tiles ? it * BN : k_begin + (it - keep_tiles) * BN; };
+  auto tile_end = [&](int it) { return it < keep_tiles ? min(keep_first, k_end) : k_end; };
 
   const KvLayout kv = make_kv_layout(k_cache, v_cache, table, kvh, num_kv_heads, page_size, page_shift, num_pages);
-  load_kv_tile<BN>(k_tiles, v_tiles, kv, k_begin, k_end, tid, PF_THREADS, status);
+  load_kv_tile<BN>(k_tiles, v_tiles, kv, tile_k0(0), tile_end(0), tid, PF_THREADS, status);
   cp_async_commit();
 
   uint32_t qf[KSTEPS][4];
@@ -281,7 +285,9 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
   for (int nt = 0; nt < NT_O; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
   // running maximum in units of the raw score, running sum; rows g and g + 8 of this warp
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
-  const float sl2 = scale * LOG2E;
+  // (capped scores are final numbers, not raw products: the exponent's scale is then 1)
+  const float sl2 = (softcap > 0.0f ? 1.0f : scale) * LOG2E;
+  const float into_cap = softcap > 0.0f ? scale / softcap : 0.0f;
   const int row_lo = warp * 16 + g, row_hi = row_lo + 8;
   const int p_row[2] = {p0 + row_lo, p0 + row_hi};
   const int lo_row[2] = {le::first_visible_key(p_row[0], reach), le::first_visible_key(p_row[1], reach)};
@@ -293,11 +299,12 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
   const int warp_lo_last = le::first_visible_key(warp_p_last, reach);
 
   for (int it = 0; it < num_tiles; ++it) {
-    const int k0 = k_begin + it * BN;
+    const int k0 = tile_k0(it);
     const int stage = it % PF_STAGES;
     if (it + 1 < num_tiles) {
       const int next = (it + 1) % PF_STAGES;
-      load_kv_tile<BN>(k_tiles + next * BN * HD, v_tiles + next * BN * HD, kv, k0 + BN, k_end, tid, PF_THREADS, status);
+      load_kv_tile<BN>(k_tiles + next * BN * HD, v_tiles + next * BN * HD, kv, tile_k0(it + 1), tile_end(it + 1), tid,
+                       PF_THREADS, status);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -313,7 +320,7 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
       }
     }
     // a warp skips tiles none of its rows can see (all keys after its last row, or all before its window)
-    const bool visible = k0 <= warp_p_last && k0 + BN - 1 >= warp_lo_first;
+    const bool visible = k0 <= warp_p_last && (k0 + BN - 1 >= warp_lo_first || it < keep_tiles);
     if (visible) {
       const bf16 *k_tile = k_tiles + stage * BN * HD, *v_tile = v_tiles + stage * BN * HD;
       float s[BN / 8][4];
@@ -324,6 +331,12 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
 #pragma unroll
         for (int nt = 0; nt < BN / 8; ++nt) s[nt][0] *= extra, s[nt][1] *= extra, s[nt][2] *= extra, s[nt][3] *= extra;
       }
+      if (softcap > 0.0f) {
+#pragma unroll
+        for (int nt = 0; nt < BN / 8; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s[nt][e] = le::capped_score(s[nt][e] * into_cap, softcap);
+      }
       // only tiles that cross the causal diagonal or the window's edge need the mask
       const bool needs_mask = k0 + BN - 1 > warp_p_first || k0 < warp_lo_last;
       if (needs_mask) {
@@ -333,7 +346,7 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
           for (int e = 0; e < 4; ++e) {
             const int r = e >> 1;
             const int pos = k0 + nt * 8 + 2 * t + (e & 1);
-            if (pos > p_row[r] || pos < lo_row[r]) s[nt][e] = -INFINITY;
+            if (!le::key_visible(pos, p_row[r], lo_row[r], keep_first)) s[nt][e] = -INFINITY;
           }
         }
       }
@@ -424,7 +437,7 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
                         const int32_t *__restrict__ cu_q, const int32_t *__restrict__ ctx_before,
                         const int32_t *__restrict__ requests, int num_heads, int num_kv_heads, int page_size,
                         int page_shift, int num_pages, int reach, float scale, const float *__restrict__ head_scale,
-                        int num_splits, int cluster_merge, int *__restrict__ status) {
+                        int keep_first, float softcap, int num_splits, int cluster_merge, int *__restrict__ status) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   // (the kernel before this one wrote the queries and the newest key and value of every request; what is
   // read before wait_for_predecessor() below is older than that: the step's integers and keys of earlier steps)
@@ -464,11 +477,19 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
     return;
   }
   const int lo = le::first_visible_key(p, reach);
-  const int total = p + 1 - lo;
+  // The keys this token reads, as one axis: the first keys that stay visible behind the window and that the window
+  // no longer holds (positions 0 .. kept - 1, padded to whole tiles: `kept_span`), then the window's keys from `lo`
+  // on.  The splits cut this axis; a tile lies on one side of the seam.  Without kept keys the axis is the positions
+  // from `lo` on, as before.
+  const int kept = min(keep_first, lo);
+  const int kept_span = (kept + DC_TILE - 1) / DC_TILE * DC_TILE;
+  const int total = kept_span + p + 1 - lo;
   int per_split = (total + num_splits - 1) / num_splits;
   per_split = (per_split + DC_TILE - 1) / DC_TILE * DC_TILE;
-  const int k_begin = lo + split * per_split;
-  const int k_end = min(p + 1, k_begin + per_split);
+  const int k_begin = split * per_split;                         // on the axis
+  const int k_end = min(total, k_begin + per_split);
+  auto position_of = [&](int u) { return u < kept_span ? u : u - kept_span + lo; };
+  auto end_position = [&](int u) { return u < kept_span ? kept : k_end - kept_span + lo; };   // where the keys of u's side end
   const int tiles_in_split = k_end > k_begin ? (k_end - k_begin + DC_TILE - 1) / DC_TILE : 0;
   const int my_tiles = tiles_in_split > warp ? (tiles_in_split - warp + DC_WARPS - 1) / DC_WARPS : 0;   // tiles warp, warp+4, ...
 
@@ -482,14 +503,15 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
   k_at.init(lane);
   v_at.init(lane);
   // pages that divide a tile and tiles that start on a page boundary take the cheap loader
-  const bool paged_tiles = page_shift >= 0 && page_size <= DC_TILE && (k_begin & (page_size - 1)) == 0;
+  const bool paged_tiles = page_shift >= 0 && page_size <= DC_TILE && (position_of(max(k_begin, kept_span)) & (page_size - 1)) == 0;
   auto load_tile = [&](int stage, int i) {
-    if (paged_tiles) load_kv_tile_warp<DC_TILE>(k_stage(stage), v_stage(stage), kv, tile_start(i), k_end, lane, status);
-    else load_kv_tile<DC_TILE>(k_stage(stage), v_stage(stage), kv, tile_start(i), k_end, lane, 32, status);
+    const int u = tile_start(i);
+    if (paged_tiles) load_kv_tile_warp<DC_TILE>(k_stage(stage), v_stage(stage), kv, position_of(u), end_position(u), lane, status);
+    else load_kv_tile<DC_TILE>(k_stage(stage), v_stage(stage), kv, position_of(u), end_position(u), lane, 32, status);
   };
   // The first tiles are asked for while the kernel before this one still runs, unless they hold the key at
   // position p, which that kernel writes.
-  auto older_than_this_step = [&](int i) { return tile_start(i) + DC_TILE <= p; };
+  auto older_than_this_step = [&](int i) { return position_of(tile_start(i)) + DC_TILE <= p; };
   bool late = false;
 #pragma unroll
   for (int s = 0; s < DC_STAGES - 1; ++s) {
@@ -524,7 +546,9 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
 #pragma unroll
   for (int nt = 0; nt < NT_O; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
-  const float sl2 = scale * LOG2E;
+  // (capped scores are final numbers, not raw products: the exponent's scale is then 1)
+  const float sl2 = (softcap > 0.0f ? 1.0f : scale) * LOG2E;
+  const float into_cap = softcap > 0.0f ? scale / softcap : 0.0f;
   const bool upper_rows = heads_here > 8;     // rows 8..15 of the MMA are padding for small groups
   // one more factor on each head's scores (rows g and g + 8 of the MMA are heads h0 + g and h0 + g + 8), applied
   // in 32 bits before the maximum (it may be negative)
@@ -541,7 +565,7 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
     if (nxt < my_tiles) load_tile(nxt % DC_STAGES, nxt);
     cp_async_commit();
     const bf16 *k_tile = k_stage(it % DC_STAGES), *v_tile = v_stage(it % DC_STAGES);
-    const int k0 = tile_start(it);
+    const int k0 = position_of(tile_start(it)), tile_end = end_position(tile_start(it));
     float s[DC_TILE / 8][4];
 #pragma unroll
     for (int nt = 0; nt < DC_TILE / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
@@ -550,13 +574,19 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
 #pragma unroll
       for (int nt = 0; nt < DC_TILE / 8; ++nt) s[nt][0] *= extra[0], s[nt][1] *= extra[0], s[nt][2] *= extra[1], s[nt][3] *= extra[1];
     }
-    const bool full = k0 + DC_TILE <= k_end;
+    if (softcap > 0.0f) {
+#pragma unroll
+      for (int nt = 0; nt < DC_TILE / 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[nt][e] = le::capped_score(s[nt][e] * into_cap, softcap);
+    }
+    const bool full = k0 + DC_TILE <= tile_end;
     if (!full) {
 #pragma unroll
       for (int nt = 0; nt < DC_TILE / 8; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e)
-          if (k0 + nt * 8 + 2 * t + (e & 1) >= k_end) s[nt][e] = -INFINITY;
+          if (k0 + nt * 8 + 2 * t + (e & 1) >= tile_end) s[nt][e] = -INFINITY;
     }
     // softmax per row in units of the raw score; rows 8..15 only when they hold heads
     float alpha[2] = {1.0f, 1.0f};
@@ -769,7 +799,8 @@ LE_API int le_attention_prefill_bf16(void *out, int64_t out_stride, const void *
                                      const void *v_cache, const int32_t *block_table, int max_blocks, const int32_t *cu_q,
                                      const int32_t *ctx_before, const int32_t *tile_request, const int32_t *tile_q0,
                                      int num_tiles, int num_heads, int num_kv_heads, int page_size, int num_pages,
-                                     int reach, float scale, const float *head_scale, int *status, cudaStream_t stream) {
+                                     int reach, float scale, const float *head_scale, int keep_first, float softcap,
+                                     int *status, cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
   if (num_kv_heads <= 0 || num_heads % num_kv_heads) return le::invalid("le_attention_prefill_bf16: %d heads do not divide into %d groups", num_heads, num_kv_heads);
   if (num_heads > 65535) return le::invalid("le_attention_prefill_bf16: too many heads for one launch");
@@ -783,7 +814,7 @@ LE_API int le_attention_prefill_bf16(void *out, int64_t out_stride, const void *
   attention_prefill_kernel<<<grid, PF_THREADS, smem, stream>>>(
       static_cast<bf16 *>(out), out_stride, static_cast<const bf16 *>(q), q_stride, static_cast<const bf16 *>(k_cache),
       static_cast<const bf16 *>(v_cache), block_table, max_blocks, cu_q, ctx_before, tile_request, tile_q0, num_heads,
-      num_kv_heads, page_size, page_shift_of(page_size), num_pages, reach, scale, head_scale, status);
+      num_kv_heads, page_size, page_shift_of(page_size), num_pages, reach, scale, head_scale, keep_first, softcap, status);
   return le::launched();
 }
 
@@ -884,7 +915,8 @@ struct DecodeForm {
   static int launch(dim3 grid, cudaStream_t stream, void *out, int64_t out_stride, float *scratch, const void *q, int64_t q_stride,
                     const void *k_cache, const void *v_cache, const int32_t *block_table, int max_blocks, const int32_t *cu_q,
                     const int32_t *ctx_before, const int32_t *requests, int num_requests, int num_heads, int num_kv_heads,
-                    int page_size, int num_pages, int reach, float scale, const float *head_scale, int num_splits, int *status) {
+                    int page_size, int num_pages, int reach, float scale, const float *head_scale, int keep_first, float softcap,
+                    int num_splits, int *status) {
     if (!ready()) return le::invalid("le_attention_decode_bf16: cannot get %zu bytes of shared memory", smem());
     if (cluster_fits(num_splits)) {
       // the splits of a (request, kv head) as one cluster: merged through shared memory, no scratch, no second kernel
@@ -893,7 +925,8 @@ struct DecodeForm {
                                         static_cast<float *>(nullptr), static_cast<const bf16 *>(q), q_stride,
                                         static_cast<const bf16 *>(k_cache), static_cast<const bf16 *>(v_cache), block_table,
                                         max_blocks, cu_q, ctx_before, requests, num_heads, num_kv_heads, page_size,
-                                        page_shift_of(page_size), num_pages, reach, scale, head_scale, num_splits, 1, status);
+                                        page_shift_of(page_size), num_pages, reach, scale, head_scale, keep_first, softcap,
+                                        num_splits, 1, status);
     }
     if (num_splits > 1 && scratch == nullptr) return le::invalid("le_attention_decode_bf16: splitting the keys %d ways needs scratch memory", num_splits);
     if (reinterpret_cast<uintptr_t>(scratch) % 8) return le::invalid("le_attention_decode_bf16: the scratch memory must start on an 8-byte boundary");
@@ -902,7 +935,8 @@ struct DecodeForm {
     int rc = le::launch_chained(attention_decode_kernel<TILE>, grid, dim3(DC_THREADS), smem(), stream, static_cast<bf16 *>(out), out_stride,
                                 part_o, part_ml, static_cast<const bf16 *>(q), q_stride, static_cast<const bf16 *>(k_cache),
                                 static_cast<const bf16 *>(v_cache), block_table, max_blocks, cu_q, ctx_before, requests, num_heads,
-                                num_kv_heads, page_size, page_shift_of(page_size), num_pages, reach, scale, head_scale, num_splits, 0, status);
+                                num_kv_heads, page_size, page_shift_of(page_size), num_pages, reach, scale, head_scale, keep_first,
+                                softcap, num_splits, 0, status);
     if (rc != 0 || num_splits == 1) return rc;
     dim3 mgrid(num_heads, num_requests);
     return le::launch_chained(attention_merge_kernel, mgrid, dim3(HD < 32 ? 32 : (HD > 128 ? 128 : HD)),
@@ -937,7 +971,8 @@ LE_API int le_attention_decode_resident_blocks(int num_splits, int small) {
 // it requests 0 .. num_requests-1 are taken.  `scratch` holds
 // le_attention_decode_scratch_floats(...) floats; it is used when the keys are
 // cut into more splits than a thread-block cluster merges by itself.
-// `reach`: see le::first_visible_key; `head_scale`: one more factor per query head on its scores, or null.
+// `reach`: see le::first_visible_key; `head_scale`: one more factor per query head on its scores, or null;
+// `keep_first`: see le::key_visible; `softcap` c > 0: a score s becomes c * tanh(s / c).
 // `form`: 0 lets the number of blocks decide between the usual form of the kernel and the one with 16-key tiles
 // (see small_form); 1 asks for the usual form, 2 for the small one where the head size has it (a caller that pads
 // the step with dummy requests knows how many of the blocks are real; the grid does not show it).
@@ -945,8 +980,8 @@ LE_API int le_attention_decode_bf16_form(void *out, int64_t out_stride, float *s
                                          const void *k_cache, const void *v_cache, const int32_t *block_table, int max_blocks,
                                          const int32_t *cu_q, const int32_t *ctx_before, const int32_t *requests,
                                          int num_requests, int num_heads, int num_kv_heads, int page_size, int num_pages,
-                                         int reach, float scale, const float *head_scale, int num_splits, int form, int *status,
-                                         cudaStream_t stream) {
+                                         int reach, float scale, const float *head_scale, int keep_first, float softcap,
+                                         int num_splits, int form, int *status, cudaStream_t stream) {
   if (num_requests <= 0) return 0;
   if (num_kv_heads <= 0 || num_heads % num_kv_heads) return le::invalid("le_attention_decode_bf16: %d heads do not divide into %d groups", num_heads, num_kv_heads);
   if (num_splits < 1 || num_splits > MERGE_MAX_SPLITS) return le::invalid("le_attention_decode_bf16: %d splits (1..%d)", num_splits, MERGE_MAX_SPLITS);
@@ -959,10 +994,10 @@ LE_API int le_attention_decode_bf16_form(void *out, int64_t out_stride, float *s
   if (small)
     return DecodeForm<16>::launch(grid, stream, out, out_stride, scratch, q, q_stride, k_cache, v_cache, block_table, max_blocks, cu_q,
                                   ctx_before, requests, num_requests, num_heads, num_kv_heads, page_size, num_pages, reach, scale,
-                                  head_scale, num_splits, status);
+                                  head_scale, keep_first, softcap, num_splits, status);
   return DecodeForm<DC_TILE_DEFAULT>::launch(grid, stream, out, out_stride, scratch, q, q_stride, k_cache, v_cache, block_table,
                                              max_blocks, cu_q, ctx_before, requests, num_requests, num_heads, num_kv_heads, page_size,
-                                             num_pages, reach, scale, head_scale, num_splits, status);
+                                             num_pages, reach, scale, head_scale, keep_first, softcap, num_splits, status);
 }
 
 LE_API int le_attention_decode_bf16(void *out, int64_t out_stride, float *scratch, const void *q, int64_t q_stride,
@@ -972,7 +1007,7 @@ LE_API int le_attention_decode_bf16(void *out, int64_t out_stride, float *scratc
                                     int window, float scale, int num_splits, int *status, cudaStream_t stream) {
   return le_attention_decode_bf16_form(out, out_stride, scratch, q, q_stride, k_cache, v_cache, block_table, max_blocks, cu_q,
                                        ctx_before, requests, num_requests, num_heads, num_kv_heads, page_size, num_pages, window,
-                                       scale, nullptr, num_splits, 0, status, stream);
+                                       scale, nullptr, 0, 0.0f, num_splits, 0, status, stream);
 }
 
 // ---------------------------------------------------------------- no allocation

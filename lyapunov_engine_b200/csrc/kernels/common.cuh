@@ -145,6 +145,12 @@ __host__ __device__ __forceinline__ int first_visible_key(int p, int reach) {
   return 0;
 }
 
+// With `keep_first` n > 0 the keys at positions below n stay visible to every later query, whatever the window or
+// chunk: a query at p sees key j <= p when j >= first_visible_key(p, reach) or j < n.
+__host__ __device__ __forceinline__ bool key_visible(int j, int p, int lo, int keep_first) {
+  return j <= p && (j >= lo || j < keep_first);
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T x);
 template <> __device__ __forceinline__ float to_f32<float>(float x) { return x; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
@@ -160,6 +166,14 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// cap * tanh(x) with x = score / cap already: capped attention scores for the bfloat16 kernels.  tanh(x) = 1 -
+// 2 / (2^(2 x log2 e) + 1) with ex2.approx and a fast division: absolute error about 1e-7 over the whole range
+// (the exponential overflows to +inf, which gives 1, and underflows to 0, which gives -1).
+__device__ __forceinline__ float capped_score(float x, float cap) {
+  const float e = fast_exp2(x * 2.8853900817779268f);
+  return cap * (1.0f - __fdividef(2.0f, e + 1.0f));
 }
 
 // Gated activations of a fused gate/up product, act(g, u), in 32 bits:

@@ -36,7 +36,8 @@
 // step of single tokens the block has no fetching warps.
 //
 // head_norm_gate_kernel: o of every (token, head) is divided by its root mean
-// square over vdim, times a weight [vdim], times silu(gate).
+// square over vdim, times a weight ([vdim], the same for every head, or [heads,
+// vdim]), times silu(gate) or sigmoid(gate), times one number.
 //
 // Everything here is 32-bit except the inputs (projections and convolution
 // outputs in the activations' type) and the gated result, which is rounded once.
@@ -314,7 +315,7 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 head_norm_gate_kernel(T *__restrict__ out, int64_t out_stride, const float *__restrict__ o, int64_t o_stride,
                       const T *__restrict__ gate, int64_t gate_stride, const float *__restrict__ weight, float eps,
-                      int num_tokens, int heads, int vdim) {
+                      int num_tokens, int heads, int vdim, int weight_per_head, int gate_kind, float out_scale) {
   le::let_successor_start();
   le::wait_for_predecessor();
   const int lane = threadIdx.x & 31;
@@ -329,9 +330,18 @@ head_norm_gate_kernel(T *__restrict__ out, int64_t out_stride, const float *__re
   const float inv = rsqrtf(ss / static_cast<float>(vdim) + eps);
   const T *gr = gate + t * gate_stride + h * vdim;
   T *dst = out + t * out_stride + h * vdim;
+  if (weight_per_head) weight += h * vdim;
+  if (gate_kind == 0 && out_scale == 1.0f) {
+    for (int i = lane; i < vdim; i += 32) {
+      const float z = le::to_f32(gr[i]);
+      dst[i] = le::from_f32<T>(x[i] * inv * weight[i] * (z / (1.0f + expf(-z))));
+    }
+    return;
+  }
   for (int i = lane; i < vdim; i += 32) {
     const float z = le::to_f32(gr[i]);
-    dst[i] = le::from_f32<T>(x[i] * inv * weight[i] * (z / (1.0f + expf(-z))));
+    const float g = gate_kind == 0 ? z / (1.0f + expf(-z)) : 1.0f / (1.0f + expf(-z));
+    dst[i] = le::from_f32<T>(x[i] * inv * weight[i] * g * out_scale);
   }
 }
 
@@ -424,15 +434,16 @@ LE_API int le_gated_delta_scan(float *out, int64_t out_stride, const void *qkv, 
   return le::invalid("le_gated_delta_scan: no kernel for %d rows a thread and %d threads a column", rows, lanes);
 }
 
-// out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight * silu(gate[t, h, :]).
+// out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight * act(gate[t, h, :]) * out_scale; weight is
+// [vdim], or [heads, vdim] with weight_per_head; act is silu (gate_kind 0) or the sigmoid (1).
 LE_API int le_head_norm_gate(void *out, int64_t out_stride, const float *o, int64_t o_stride, const void *gate,
                              int64_t gate_stride, int dtype, const float *weight, float eps, int num_tokens, int heads,
-                             int vdim, cudaStream_t stream) {
+                             int vdim, int weight_per_head, int gate_kind, float out_scale, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   const int64_t items = static_cast<int64_t>(num_tokens) * heads;
   const dim3 grid(static_cast<unsigned>((items + 3) / 4));
   LE_DISPATCH_DTYPE(dtype, T,
                     return le::launch_chained(head_norm_gate_kernel<T>, grid, dim3(128), 0, stream, static_cast<T *>(out),
                                               out_stride, o, o_stride, static_cast<const T *>(gate), gate_stride, weight,
-                                              eps, num_tokens, heads, vdim));
+                                              eps, num_tokens, heads, vdim, weight_per_head, gate_kind, out_scale));
 }

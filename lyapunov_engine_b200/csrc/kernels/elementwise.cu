@@ -14,7 +14,7 @@ namespace {
 // writes zeros instead of reading out of bounds.
 template <typename T>
 __global__ void embed_kernel(float *__restrict__ out, const T *__restrict__ table, const int32_t *__restrict__ ids,
-                             int hidden, int vocab, int *__restrict__ status) {
+                             int hidden, int vocab, float scale, int *__restrict__ status) {
   le::let_successor_start();
   le::wait_for_predecessor();
   const int t = blockIdx.x;
@@ -26,7 +26,11 @@ __global__ void embed_kernel(float *__restrict__ out, const T *__restrict__ tabl
     return;
   }
   const T *src = table + static_cast<int64_t>(id) * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = le::to_f32(src[i]);
+  if (scale == 1.0f) {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = le::to_f32(src[i]);
+  } else {       // (one factor on the whole table, applied in 32 bits)
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = le::to_f32(src[i]) * scale;
+  }
 }
 
 // The same with a sinusoidal position vector added in 32 bits: for the token at
@@ -94,6 +98,31 @@ __global__ void head_gate_kernel(T *__restrict__ x, int64_t x_stride, const T *_
 #pragma unroll
     for (int v = 0; v < VEC; ++v) e[v] = le::from_f32<T>(le::to_f32(e[v]) * s);
     *reinterpret_cast<uint4 *>(p) = raw;
+  }
+}
+
+// out[t, i] = x[t, i] * sigmoid(gate[t, i]) * scale: a gate of its own for every entry; 32-bit, rounded once.
+template <typename T, int VEC>
+__global__ void sigmoid_gate_kernel(T *__restrict__ out, int64_t out_stride, const T *__restrict__ x, int64_t x_stride,
+                                    const T *__restrict__ gate, int64_t gate_stride, int num_tokens, int width, float scale) {
+  le::let_successor_start();
+  le::wait_for_predecessor();
+  const int per_row = width / VEC;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<int64_t>(num_tokens) * per_row) return;
+  const int64_t t = idx / per_row;
+  const int i = static_cast<int>(idx - t * per_row) * VEC;
+  if constexpr (VEC == 1) {
+    const float g = le::to_f32(gate[t * gate_stride + i]);
+    out[t * out_stride + i] = le::from_f32<T>(le::to_f32(x[t * x_stride + i]) * (scale / (1.0f + expf(-g))));
+  } else {
+    uint4 xr = *reinterpret_cast<const uint4 *>(x + t * x_stride + i);
+    const uint4 gr = *reinterpret_cast<const uint4 *>(gate + t * gate_stride + i);
+    T *xe = reinterpret_cast<T *>(&xr);
+    const T *ge = reinterpret_cast<const T *>(&gr);
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) xe[v] = le::from_f32<T>(le::to_f32(xe[v]) * (scale / (1.0f + expf(-le::to_f32(ge[v])))));
+    *reinterpret_cast<uint4 *>(out + t * out_stride + i) = xr;
   }
 }
 
@@ -197,12 +226,12 @@ LE_API int le_zero_fresh_states(const void *table, int num_buffers, int num_rows
 }
 
 LE_API int le_embed(float *out, const void *table, int table_dtype, const int32_t *ids, int num_tokens, int hidden,
-                    int vocab, int *status, cudaStream_t stream) {
+                    int vocab, float scale, int *status, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
   LE_DISPATCH_DTYPE(table_dtype, T,
                     return le::launch_chained(embed_kernel<T>, dim3(num_tokens), dim3(threads), 0, stream, out,
-                                              static_cast<const T *>(table), ids, hidden, vocab, status));
+                                              static_cast<const T *>(table), ids, hidden, vocab, scale, status));
 }
 
 // The embedding with the sinusoidal position vector (see embed_sinusoid_kernel).
@@ -256,6 +285,26 @@ LE_API int le_head_gate(void *x, int64_t x_stride, const void *gate, int64_t gat
   else return le::invalid("le_head_gate: unknown dtype code %d", dtype);
 #undef LE_GO
   return le::launched();
+}
+
+// out, x, gate: [T, width] with row strides of their own (column ranges of wider rows are fine; out may be x).
+LE_API int le_sigmoid_gate(void *out, int64_t out_stride, const void *x, int64_t x_stride, const void *gate,
+                           int64_t gate_stride, int dtype, int num_tokens, int width, float scale, cudaStream_t stream) {
+  if (num_tokens <= 0 || width <= 0) return 0;
+  const int vec = dtype == LE_BF16 ? 8 : 4;
+  const bool wide = width % vec == 0 && out_stride % vec == 0 && x_stride % vec == 0 && gate_stride % vec == 0 &&
+                    ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(gate)) & 15) == 0;
+  const int64_t items = static_cast<int64_t>(num_tokens) * width / (wide ? vec : 1);
+  const int64_t blocks = (items + 255) / 256;
+  if (blocks > 2147483647LL) return le::invalid("le_sigmoid_gate: too many elements for one launch");
+#define LE_GO(T, V)                                                                                                       \
+  return le::launch_chained(sigmoid_gate_kernel<T, V>, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream,         \
+                            static_cast<T *>(out), out_stride, static_cast<const T *>(x), x_stride,                       \
+                            static_cast<const T *>(gate), gate_stride, num_tokens, width, scale)
+  if (dtype == LE_BF16) { if (wide) LE_GO(__nv_bfloat16, 8); LE_GO(__nv_bfloat16, 1); }
+  if (dtype == LE_F32) { if (wide) LE_GO(float, 4); LE_GO(float, 1); }
+#undef LE_GO
+  return le::invalid("le_sigmoid_gate: unknown dtype code %d", dtype);
 }
 
 LE_API int le_swiglu(void *out, const void *gate_up, int dtype, int num_tokens, int inter, cudaStream_t stream) {

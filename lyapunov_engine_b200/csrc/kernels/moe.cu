@@ -17,7 +17,9 @@
 //          up), F wide.  Input rows are gathered through `src_of_slot` divided
 //          by `src_div` (pairs -> tokens) or are the sorted slots themselves;
 //          output rows go to the sorted slot or are scattered back to the pair
-//          with the pair's weight as a factor (float32 output).
+//          with the pair's weight as a factor (float32 output).  In the gated
+//          form a pair's weight is the factor on the expert's input instead:
+//          both products are multiplied by it, in 32 bits, before the activation.
 // combine: out[t] = sum_j y[t * top + j] (+ gate[t] * shared[t]).
 // Where experts have many rows each (prompt portions, bfloat16) the products run on the tcgen05 kernel of
 // gemm_tc.cu in its grouped form instead: the grouping pads every expert's slots to whole tiles of 128, the rows of
@@ -121,9 +123,10 @@ moe_logits_kernel(const T *__restrict__ h, int64_t h_stride, const float *__rest
 }
 
 // The choice: a warp per token picks the `top` largest of its logits (ties: the lower index), writes their ids and
-// the softmax over them, and the shared gate's sigmoid.  It marks what it has picked in z.
+// the softmax over them (`scoring` 0) or each one's own sigmoid (`scoring` 1), and the shared gate's sigmoid.  It
+// marks what it has picked in z.
 __global__ void moe_pick_kernel(float *__restrict__ z, int32_t *__restrict__ ids, float *__restrict__ weights,
-                                float *__restrict__ gate, int tokens, int experts, int top, int with_gate) {
+                                float *__restrict__ gate, int tokens, int experts, int top, int with_gate, int scoring) {
   le::let_successor_start();
   le::wait_for_predecessor();
   const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
@@ -146,7 +149,8 @@ __global__ void moe_pick_kernel(float *__restrict__ z, int32_t *__restrict__ ids
     }
     if (at == 0x7fffffff) at = 0;   // (no finite logit left: cannot happen with top <= experts)
     if (j == 0) first = best;
-    const float p = expf(best - first);
+    // scoring 1: the weight is the chosen logit's sigmoid by itself (the largest logits are the largest scores)
+    const float p = scoring == 1 ? 1.0f / (1.0f + expf(-best)) : expf(best - first);
     total += p;
     if (lane == 0) {
       ids[static_cast<int64_t>(t) * top + j] = at;
@@ -155,6 +159,7 @@ __global__ void moe_pick_kernel(float *__restrict__ z, int32_t *__restrict__ ids
     }
     __syncwarp();
   }
+  if (scoring == 1) return;
   for (int j = lane; j < top; j += 32) weights[static_cast<int64_t>(t) * top + j] /= total;
 }
 
@@ -236,12 +241,13 @@ __global__ void moe_group_kernel(const int32_t *__restrict__ ids, int pairs, int
   }
 }
 
-// Rows of x gathered into slot order (16-byte pieces): out[slot] = x[slot_pair[slot] / src_div], zeros for slots that
-// stand for no pair; only the first meta[0] * tile_m slots are touched.
+// Rows of x gathered into slot order (16-byte pieces): out[slot] = x[slot_pair[slot] / src_div] (times the pair's
+// weight where `pair_weight` is given), zeros for slots that stand for no pair; only the first meta[0] * tile_m
+// slots are touched.
 template <typename T>
 __global__ void moe_gather_kernel(T *__restrict__ out, const T *__restrict__ x, int64_t x_stride,
                                   const int32_t *__restrict__ slot_pair, int src_div, int tile_m,
-                                  const int32_t *__restrict__ meta, int width) {
+                                  const int32_t *__restrict__ meta, int width, const float *__restrict__ pair_weight) {
   le::let_successor_start();
   le::wait_for_predecessor();
   const int slot = blockIdx.x;
@@ -250,6 +256,17 @@ __global__ void moe_gather_kernel(T *__restrict__ out, const T *__restrict__ x, 
   constexpr int PIECE = 16 / sizeof(T);
   uint4 *dst = reinterpret_cast<uint4 *>(out + static_cast<int64_t>(slot) * width);
   const uint4 *src = pair >= 0 ? reinterpret_cast<const uint4 *>(x + static_cast<int64_t>(pair / src_div) * x_stride) : nullptr;
+  if (pair_weight != nullptr && src != nullptr) {      // the row times the pair's weight, rounded once
+    const float f = pair_weight[pair];
+    for (int i = threadIdx.x; i < width / PIECE; i += blockDim.x) {
+      uint4 raw = src[i];
+      T *e = reinterpret_cast<T *>(&raw);
+#pragma unroll
+      for (int v = 0; v < PIECE; ++v) e[v] = le::from_f32<T>(le::to_f32(e[v]) * f);
+      dst[i] = raw;
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < width / PIECE; i += blockDim.x) dst[i] = src != nullptr ? src[i] : make_uint4(0, 0, 0, 0);
 }
 
@@ -266,7 +283,8 @@ __global__ void moe_combine_sorted_kernel(T *__restrict__ out, const TY *__restr
   const int64_t t = i / width, c = i - t * width;
   float acc = 0.0f;
   for (int j = 0; j < top; ++j)
-    acc = fmaf(share[t * top + j], le::to_f32(y[static_cast<int64_t>(pair_slot[t * top + j]) * width + c]), acc);
+    acc = fmaf(share != nullptr ? share[t * top + j] : 1.0f,
+               le::to_f32(y[static_cast<int64_t>(pair_slot[t * top + j]) * width + c]), acc);
   if (shared_out != nullptr) acc = fmaf(gate != nullptr ? gate[t] : 1.0f, le::to_f32(shared_out[i]), acc);
   out[i] = le::from_f32<T>(acc);
 }
@@ -345,8 +363,13 @@ __global__ void moe_grouped_kernel(TOut *__restrict__ out, int64_t out_stride, c
       const int n = n0 + tx * 4 + j;
       if (n >= N) continue;
       float v = acc[i][j];
-      if constexpr (GATED) v = le::gated_activation(v, acc_up[i][j], act);
-      o[n] = le::from_f32<TOut>(v * row_factor[m]);
+      if constexpr (GATED) {
+        // (the pair's weight is the factor on the expert's input: both products carry it into the activation)
+        v = le::gated_activation(v * row_factor[m], acc_up[i][j] * row_factor[m], act);
+        o[n] = le::from_f32<TOut>(v);
+      } else {
+        o[n] = le::from_f32<TOut>(v * row_factor[m]);
+      }
     }
   }
 }
@@ -505,8 +528,12 @@ moe_grouped_mma_kernel(TOut *__restrict__ out, int64_t out_stride, const __nv_bf
           const int n = n0 + wn + nt * 8 + 2 * t4 + j;
           if (n >= N) continue;
           float v = acc[0][mt][nt][half * 2 + j];
-          if constexpr (GATED) v = le::gated_activation(v, acc[1][mt][nt][half * 2 + j], act);
-          o[n] = le::from_f32<TOut>(v * f);
+          if constexpr (GATED) {
+            v = le::gated_activation(v * f, acc[1][mt][nt][half * 2 + j] * f, act);
+            o[n] = le::from_f32<TOut>(v);
+          } else {
+            o[n] = le::from_f32<TOut>(v * f);
+          }
         }
     }
 }
@@ -548,7 +575,7 @@ LE_API int le_moe_tile_rows(int wide) { return wide ? TILE_M_WIDE : TILE_M; }
 // `z`: float32 scratch [tokens, experts + 1] (the logits; the picked ones are overwritten).
 LE_API int le_moe_route(const void *h, int64_t h_stride, int dtype, const float *w_router, const float *b_router,
                         const float *w_gate, float *z, int32_t *ids, float *weights, float *gate, int tokens, int width,
-                        int experts, int top, cudaStream_t stream) {
+                        int experts, int top, int scoring, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (top < 1 || top > experts) return le::invalid("le_moe_route: %d of %d experts", top, experts);
   // tokens a block takes: up to 8, fewer where the step has fewer or a row is wide
@@ -575,8 +602,9 @@ LE_API int le_moe_route(const void *h, int64_t h_stride, int dtype, const float 
   }
 #undef LE_LOGITS
   if (rc != 0) return rc;
+  if (scoring != 0 && scoring != 1) return le::invalid("le_moe_route: scoring %d is neither 0 (softmax over the chosen) nor 1 (sigmoid)", scoring);
   return le::launch_chained(moe_pick_kernel, dim3((tokens + 7) / 8), dim3(256), 0, stream, z, ids, weights, gate, tokens, experts,
-                            top, w_gate != nullptr ? 1 : 0);
+                            top, w_gate != nullptr ? 1 : 0, scoring);
 }
 
 LE_API int le_moe_group(const int32_t *ids, int pairs, int experts, int tile_m, int padded, int max_tiles, int slots_cap,
@@ -592,7 +620,8 @@ LE_API int le_moe_group(const int32_t *ids, int pairs, int experts, int tile_m, 
 }
 
 LE_API int le_moe_gather(void *out, const void *x, int64_t x_stride, int dtype, const int32_t *slot_pair, int src_div,
-                         int tile_m, const int32_t *meta, int slots_cap, int width, cudaStream_t stream) {
+                         int tile_m, const int32_t *meta, int slots_cap, int width, const float *pair_weight,
+                         cudaStream_t stream) {
   if (slots_cap <= 0) return 0;
   const int piece = dtype == LE_BF16 ? 8 : 4;
   if (width % piece || x_stride % piece || reinterpret_cast<uintptr_t>(out) % 16 || reinterpret_cast<uintptr_t>(x) % 16)
@@ -600,9 +629,9 @@ LE_API int le_moe_gather(void *out, const void *x, int64_t x_stride, int dtype, 
   if (dtype == LE_BF16)
     return le::launch_chained(moe_gather_kernel<__nv_bfloat16>, dim3(slots_cap), dim3(128), 0, stream,
                               static_cast<__nv_bfloat16 *>(out), static_cast<const __nv_bfloat16 *>(x), x_stride, slot_pair,
-                              src_div, tile_m, meta, width);
+                              src_div, tile_m, meta, width, pair_weight);
   return le::launch_chained(moe_gather_kernel<float>, dim3(slots_cap), dim3(128), 0, stream, static_cast<float *>(out),
-                            static_cast<const float *>(x), x_stride, slot_pair, src_div, tile_m, meta, width);
+                            static_cast<const float *>(x), x_stride, slot_pair, src_div, tile_m, meta, width, pair_weight);
 }
 
 LE_API int le_moe_combine_sorted(void *out, int dtype, const void *y, int y_dtype, const int32_t *pair_slot,

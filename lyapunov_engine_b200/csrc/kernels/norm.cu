@@ -3,6 +3,9 @@
 //   resid[r] += delta[0][r] + delta[1][r] + ...   (when delta is given)
 //   out[r]    = resid[r] * rsqrt(mean(resid[r]^2) + eps) * weight
 //
+// With `delta_scale` (one number per column) the sum of the deltas is multiplied by it, in 32 bits, before it
+// enters the stream: resid[r] += delta_scale * (delta[0][r] + ...).
+//
 // With `groups` > 1 a row is cut into that many equal consecutive parts and
 // each part is divided by its own root mean square (one block per row and part).
 //
@@ -63,6 +66,7 @@ __device__ __forceinline__ void store_vec(T *p, const float (&src)[VEC]) {
 }
 
 struct TapsArgs {
+  const float *delta_scale = nullptr;   // [row width]: a factor per column on what enters the stream (rides here: every form gets it)
   const float *w = nullptr;        // [taps, channels]
   float *state = nullptr;          // [num_state_rows, taps - 1, channels]
   const int32_t *slots = nullptr;  // state row of each request (< 0: none; zeros before it, nothing kept)
@@ -178,6 +182,7 @@ __global__ void rmsnorm_kernel(TO *__restrict__ out, float *__restrict__ resid, 
   TO *o = out + static_cast<int64_t>(blockIdx.x) * row_width + part;
   weight += part;
   const bool write_back = (d != nullptr) && (rows == nullptr);
+  const float *dscale = taps.delta_scale ? taps.delta_scale + part : nullptr;
 
   if constexpr (PER_THREAD > 0 && PARTIALS > 0) {
     float val[PER_THREAD][VEC], add[PER_THREAD][PARTIALS][VEC], w[PER_THREAD][VEC];
@@ -209,11 +214,21 @@ __global__ void rmsnorm_kernel(TO *__restrict__ out, float *__restrict__ resid, 
     for (int it = 0; it < PER_THREAD; ++it) {
       const int i = (it * blockDim.x + threadIdx.x) * VEC;
       if (i < hidden) {
-        if (d) {
+        if (d && dscale == nullptr) {
 #pragma unroll
           for (int p = 0; p < PARTIALS; ++p)       // in the partial sums' order, as the general form adds them
 #pragma unroll
             for (int v = 0; v < VEC; ++v) val[it][v] += add[it][p][v];
+        } else if (d) {
+          float sc[VEC];
+          load_vec<float, VEC>(sc, dscale + i);
+#pragma unroll
+          for (int v = 0; v < VEC; ++v) {
+            float sum = add[it][0][v];
+#pragma unroll
+            for (int p = 1; p < PARTIALS; ++p) sum += add[it][p][v];
+            val[it][v] = fmaf(sc[v], sum, val[it][v]);
+          }
         }
         if (write_back) store_vec<float, VEC>(x + i, val[it]);
 #pragma unroll
@@ -245,13 +260,26 @@ __global__ void rmsnorm_kernel(TO *__restrict__ out, float *__restrict__ resid, 
       const int i = (it * blockDim.x + threadIdx.x) * VEC;
       if (i < hidden) {
         load_vec<float, VEC>(val[it], x + i);
-        if (d)
+        if (d && dscale == nullptr) {
           for (int p = 0; p < num_partials; ++p) {
             float add[VEC];
             load_vec<TD, VEC>(add, d + p * partial_stride + i);
 #pragma unroll
             for (int v = 0; v < VEC; ++v) val[it][v] += add[v];
           }
+        } else if (d) {
+          float sum[VEC], sc[VEC];
+          load_vec<TD, VEC>(sum, d + i);
+          for (int p = 1; p < num_partials; ++p) {
+            float add[VEC];
+            load_vec<TD, VEC>(add, d + p * partial_stride + i);
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) sum[v] += add[v];
+          }
+          load_vec<float, VEC>(sc, dscale + i);
+#pragma unroll
+          for (int v = 0; v < VEC; ++v) val[it][v] = fmaf(sc[v], sum[v], val[it][v]);
+        }
         if (write_back) store_vec<float, VEC>(x + i, val[it]);
 #pragma unroll
         for (int v = 0; v < VEC; ++v) ss += val[it][v] * val[it][v];
@@ -279,8 +307,13 @@ __global__ void rmsnorm_kernel(TO *__restrict__ out, float *__restrict__ resid, 
 #pragma unroll
     for (int v = 0; v < VEC; ++v) {
       float val = x[i + v];
-      if (d)
+      if (d && dscale == nullptr) {
         for (int p = 0; p < num_partials; ++p) val += le::to_f32(d[p * partial_stride + i + v]);
+      } else if (d) {
+        float sum = le::to_f32(d[i + v]);
+        for (int p = 1; p < num_partials; ++p) sum += le::to_f32(d[p * partial_stride + i + v]);
+        val = fmaf(dscale[i + v], sum, val);
+      }
       if (write_back) x[i + v] = val;
       ss += val * val;
     }
@@ -291,8 +324,13 @@ __global__ void rmsnorm_kernel(TO *__restrict__ out, float *__restrict__ resid, 
 #pragma unroll
     for (int v = 0; v < VEC; ++v) {
       float val = x[i + v];
-      if (d && !write_back)
+      if (d && !write_back && dscale == nullptr) {
         for (int p = 0; p < num_partials; ++p) val += le::to_f32(d[p * partial_stride + i + v]);
+      } else if (d && !write_back) {
+        float sum = le::to_f32(d[i + v]);
+        for (int p = 1; p < num_partials; ++p) sum += le::to_f32(d[p * partial_stride + i + v]);
+        val = fmaf(dscale[i + v], sum, val);
+      }
       o[i + v] = le::from_f32<TO>(val * inv * weight[i + v]);
     }
   }
@@ -345,16 +383,18 @@ int launch(void *out, float *resid, const void *delta, int num_partials, int64_t
 // `groups`: equal consecutive parts of a row, each with its own root mean square (1: the whole row).
 // `out_dtype` is the type of `out`; `delta_dtype` that of `delta`, which holds
 // `num_partials` tensors of the residual stream's shape, `partial_stride`
-// elements apart.
+// elements apart.  `delta_scale`: float32 [hidden] or null, the factor per column on the deltas' sum.
 LE_API int le_rmsnorm(void *out, int out_dtype, float *resid, const void *delta, int delta_dtype, int num_partials,
                       int64_t partial_stride, const float *weight, const int32_t *rows, float eps, int num_rows, int hidden,
-                      int groups, cudaStream_t stream) {
+                      int groups, const float *delta_scale, cudaStream_t stream) {
   if (num_rows <= 0) return 0;
   if (hidden <= 0) return le::invalid("le_rmsnorm: hidden must be positive");
   if (groups < 1 || groups > 65535 || hidden % groups)
     return le::invalid("le_rmsnorm: a row of %d values does not divide into %d equal parts", hidden, groups);
   if (delta != nullptr && num_partials < 1) return le::invalid("le_rmsnorm: num_partials must be at least 1");
-  const TapsArgs taps{};
+  if (delta_scale != nullptr && (reinterpret_cast<uintptr_t>(delta_scale) & 15)) return le::invalid("le_rmsnorm: delta_scale must be 16-byte aligned");
+  TapsArgs taps{};
+  taps.delta_scale = delta != nullptr ? delta_scale : nullptr;
 #define LE_GO(TO, TD) return launch<TO, TD>(out, resid, delta, num_partials, partial_stride, weight, rows, eps, num_rows, hidden, groups, taps, stream)
   if (out_dtype == LE_F32 && (delta == nullptr || delta_dtype == LE_F32)) LE_GO(float, float);
   if (out_dtype == LE_BF16 && (delta == nullptr || delta_dtype == LE_BF16)) LE_GO(__nv_bfloat16, __nv_bfloat16);

@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(CONV_THREADS)
 short_conv_kernel(T *__restrict__ out, const T *__restrict__ h, const float *__restrict__ w, float *__restrict__ state,
                   int num_state_rows, const int32_t *__restrict__ state_slots, const int32_t *__restrict__ cu_q,
                   const int32_t *__restrict__ tile_request, const int32_t *__restrict__ tile_q0, int channels, int taps,
-                  int64_t h_stride, int add_input, int activation) {
+                  int64_t h_stride, int add_input, int activation, const float *__restrict__ bias) {
   le::let_successor_start();
   const int r = threadIdx.x / CONV_LANES;                                   // this thread's token within the tile
   const int c = (blockIdx.y * CONV_LANES + threadIdx.x % CONV_LANES) * VEC;  // its first channel
@@ -113,6 +113,12 @@ short_conv_kernel(T *__restrict__ out, const T *__restrict__ h, const float *__r
 #pragma unroll
       for (int e = 0; e < VEC; ++e) acc[e] = 0.0f;
     }
+    if (bias != nullptr) {       // one number per channel, the sum's first term
+      float bv[VEC];
+      load_channels<float, VEC>(bv, bias + c);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc[e] += bv[e];
+    }
     for (int j = 0; j < taps; ++j) {
       const int src = q - (keep - j);
       float v[VEC], wt[VEC];
@@ -145,11 +151,11 @@ short_conv_kernel(T *__restrict__ out, const T *__restrict__ h, const float *__r
 
 // The general form: rows of h are h_stride elements apart (the channels are the first `channels` columns of wider
 // rows); add_input 0 leaves the token's own input out of the sum (a plain convolution, whose last tap is the current
-// token's); activation 1 puts silu over the sum.
+// token's); activation 1 puts silu over the sum; bias (float32 [channels] or null) is added to the sum.
 LE_API int le_short_conv_general(void *out, const void *h, int64_t h_stride, int dtype, const float *w, float *state,
                                  int num_state_rows, const int32_t *state_slots, const int32_t *cu_q,
                                  const int32_t *tile_request, const int32_t *tile_q0, int num_tiles, int tile, int channels,
-                                 int taps, int add_input, int activation, cudaStream_t stream);
+                                 int taps, int add_input, int activation, const float *bias, cudaStream_t stream);
 
 // out, h: [tokens, channels] contiguous (different buffers); w: [taps, channels] float32; state:
 // [num_state_rows, taps - 1, channels] float32 (may be null when taps is 1); the tiles list `tile` tokens each.
@@ -158,13 +164,13 @@ LE_API int le_short_conv(void *out, const void *h, int dtype, const float *w, fl
                          const int32_t *state_slots, const int32_t *cu_q, const int32_t *tile_request,
                          const int32_t *tile_q0, int num_tiles, int tile, int channels, int taps, cudaStream_t stream) {
   return le_short_conv_general(out, h, channels, dtype, w, state, num_state_rows, state_slots, cu_q, tile_request, tile_q0,
-                               num_tiles, tile, channels, taps, 1, 0, stream);
+                               num_tiles, tile, channels, taps, 1, 0, nullptr, stream);
 }
 
 LE_API int le_short_conv_general(void *out, const void *h, int64_t h_stride, int dtype, const float *w, float *state,
                                  int num_state_rows, const int32_t *state_slots, const int32_t *cu_q,
                                  const int32_t *tile_request, const int32_t *tile_q0, int num_tiles, int tile, int channels,
-                                 int taps, int add_input, int activation, cudaStream_t stream) {
+                                 int taps, int add_input, int activation, const float *bias, cudaStream_t stream) {
   if (num_tiles <= 0 || channels <= 0) return 0;
   if (h_stride < channels) return le::invalid("le_short_conv: rows of %lld elements hold no %d channels", (long long)h_stride, channels);
   if (taps < 1 || taps > CONV_MAX_TAPS) return le::invalid("le_short_conv: taps must be 1..%d, got %d", CONV_MAX_TAPS, taps);
@@ -175,14 +181,14 @@ LE_API int le_short_conv_general(void *out, const void *h, int64_t h_stride, int
   // 16-byte accesses to the rows (vec values of the type) and to weights and state (two or one of them per access)
   const bool wide = channels % 8 == 0 && h_stride % 8 == 0 &&
                     ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(w) |
-                      reinterpret_cast<uintptr_t>(state)) & 15) == 0;
+                      reinterpret_cast<uintptr_t>(state) | reinterpret_cast<uintptr_t>(bias)) & 15) == 0;
   const int per_block = CONV_LANES * (wide ? vec : 1);
   const dim3 grid(num_tiles, (channels + per_block - 1) / per_block);
   if (grid.y > 65535) return le::invalid("le_short_conv: too many channels for one launch");
 #define LE_GO(T, V)                                                                                                  \
   return le::launch_chained(short_conv_kernel<T, V>, grid, dim3(CONV_THREADS), 0, stream, static_cast<T *>(out),     \
                             static_cast<const T *>(h), w, state, num_state_rows, state_slots, cu_q, tile_request,    \
-                            tile_q0, channels, taps, h_stride, add_input, activation)
+                            tile_q0, channels, taps, h_stride, add_input, activation, bias)
   if (dtype == LE_BF16) { if (wide) LE_GO(__nv_bfloat16, 8); LE_GO(__nv_bfloat16, 1); }
   if (dtype == LE_F32) { if (wide) LE_GO(float, 4); LE_GO(float, 1); }
 #undef LE_GO

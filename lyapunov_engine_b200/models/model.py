@@ -23,6 +23,7 @@ class CacheGroupPlan:
     window: int | None
     chunk: int | None = None
     values: bool = True      # False: one pool per run serves as keys and as values
+    keep_first: int = 0      # keys at positions below this stay visible behind a window: their pages are never given back
 
 
 @dataclass(frozen=True)
@@ -74,7 +75,7 @@ class Model:
                         raise ValueError(f"run order entry {index} cannot read the cache of entry {src}: different geometry")
                     group, stream, writes = other.group, other.stream, False
                 else:
-                    plan = CacheGroupPlan(need.num_kv_heads, need.head_dim, need.window, need.chunk, need.values)
+                    plan = CacheGroupPlan(need.num_kv_heads, need.head_dim, need.window, need.chunk, need.values, need.keep_first)
                     if plan not in self.groups:
                         self.groups.append(plan)
                         self.streams_per_group.append(0)

@@ -64,14 +64,14 @@ _core = None
 _attention: dict[int, ctypes.CDLL] = {}
 
 _CORE_SIGNATURES = {
-    "le_embed": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    "le_embed": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "le_zero_fresh_state": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p],
     "le_zero_fresh_states": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
     "le_sm_count": [],
     "le_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "le_convert": [c_void_p, c_int, c_void_p, c_int, c_int64, c_void_p],
     "le_rmsnorm": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p, c_float, c_int,
-                   c_int, c_int, c_void_p],
+                   c_int, c_int, c_void_p, c_void_p],
     "le_rmsnorm_taps_applies": [c_int, c_int],
     "le_rmsnorm_taps": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_float, c_int, c_int, c_int,
                         c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p],
@@ -81,7 +81,7 @@ _CORE_SIGNATURES = {
     "le_short_conv": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                       c_int, c_int, c_int, c_void_p],
     "le_short_conv_general": [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "le_glu_bias": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p],
     "le_gated_delta_lanes": [c_int],
     "le_gated_delta_scratch": [c_int, c_int],
@@ -89,7 +89,7 @@ _CORE_SIGNATURES = {
                             c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                             c_float, c_float, c_void_p, c_void_p],
     "le_head_norm_gate": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p, c_float, c_int, c_int,
-                          c_int, c_void_p],
+                          c_int, c_int, c_int, c_float, c_void_p],
     "le_rope_norm_store": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_int,
                            c_void_p, c_void_p],
@@ -103,6 +103,18 @@ _CORE_SIGNATURES = {
     "le_gate_rows": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64, c_int, c_void_p, c_int, c_int, c_int, c_void_p,
                      c_void_p],
     "le_stream_entry": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p],
+    "le_sigmoid_gate": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_float, c_void_p],
+    "le_ssm_scan_lanes": [c_int],
+    "le_ssm_scan_rows_per_block": [c_int, c_int],
+    "le_ssm_scan": [c_void_p, c_int, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p,
+                    c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                    c_int, c_int, c_int, c_float, c_void_p],
+    "le_mlstm_rows": [c_int, c_int],
+    "le_mlstm_scan": [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                      c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
+    "le_rope_qknorm_store": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_int,
+                             c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                             c_int, c_int, c_int, c_void_p, c_void_p],
     "le_kv_store": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                     c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "le_latent_norm_store": [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p,
@@ -137,10 +149,10 @@ _CORE_SIGNATURES = {
     "le_softcap": [c_void_p, c_int64, c_float, c_void_p],
     "le_moe_tile_rows": [c_int],
     "le_moe_route": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                     c_int, c_int, c_int, c_void_p],
+                     c_int, c_int, c_int, c_int, c_void_p],
     "le_moe_group": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                      c_void_p, c_void_p],
-    "le_moe_gather": [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
+    "le_moe_gather": [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "le_moe_combine_sorted": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                               c_void_p],
     "le_gemm_tc_grouped_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int,
@@ -156,7 +168,7 @@ _CORE_SIGNATURES = {
 _ATTENTION_SIGNATURES = {
     "le_attention_generic": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int,
                              c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                             c_float, c_void_p, c_void_p, c_void_p],
+                             c_float, c_void_p, c_int, c_float, c_void_p, c_void_p],
 }
 
 
@@ -198,7 +210,7 @@ def attention_lib(head_dim: int):
 _EXTRA_ATTENTION_SIGNATURES: dict[str, list] = {
     "le_attention_prefill_bf16": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                                  c_void_p, c_void_p, c_void_p],
+                                  c_void_p, c_int, c_float, c_void_p, c_void_p],
     "le_attention_prefill_tc_bf16": [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                      c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                      c_int, c_float, c_void_p, c_void_p, c_void_p],
@@ -207,7 +219,7 @@ _EXTRA_ATTENTION_SIGNATURES: dict[str, list] = {
                                  c_int, c_void_p, c_void_p],
     "le_attention_decode_bf16_form": [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
                                       c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                                      c_void_p, c_int, c_int, c_void_p, c_void_p],
+                                      c_void_p, c_int, c_float, c_int, c_int, c_void_p, c_void_p],
 }
 
 
@@ -242,14 +254,14 @@ def check_status(status: torch.Tensor) -> None:
 
 
 # --------------------------------------------------------------------------
-def embed(out_resid: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor) -> None:
-    """out_resid[t] (float32) = table[ids[t]]."""
+def embed(out_resid: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor, scale: float = 1.0) -> None:
+    """out_resid[t] (float32) = table[ids[t]] * scale."""
     _need_cuda(out_resid, table, ids)
     T, H = out_resid.shape
     assert out_resid.dtype == torch.float32 and ids.dtype == torch.int32 and table.shape[1] == H
     assert out_resid.is_contiguous() and table.is_contiguous()
     _check(core().le_embed(_ptr(out_resid), _ptr(table), dtype_code(table.dtype), _ptr(ids), T, H, table.shape[0],
-                           _ptr(status), _stream()), "le_embed")
+                           float(scale), _ptr(status), _stream()), "le_embed")
 
 
 def zero_fresh_state(state: torch.Tensor, state_slots: torch.Tensor, ctx_before: torch.Tensor, num_requests: int) -> None:
@@ -455,17 +467,19 @@ def convert(out: torch.Tensor, src: torch.Tensor) -> None:
 
 
 def rmsnorm(out: torch.Tensor, resid: torch.Tensor, delta, weight: torch.Tensor, eps: float, rows=None,
-            groups: int = 1) -> None:
+            groups: int = 1, delta_scale=None) -> None:
     """resid += delta (when given and ``rows`` is None); out = rmsnorm(resid) * weight.
+    ``delta_scale`` (float32 [H]): resid += delta_scale * delta instead.
     ``groups`` > 1: each of that many equal consecutive parts of a row is
     divided by its own root mean square.
     ``delta`` has the residual stream's shape [T, H] in the activations' type,
     or is float32 [S, T, H]: the partial sums of a split-K product, added in
     order.  With ``rows`` (int32 indices) only those rows are normed, into
     out[0..len(rows)), and ``resid`` is left as it is."""
-    _need_cuda(out, resid, delta, weight, rows)
+    _need_cuda(out, resid, delta, weight, rows, delta_scale)
     H = resid.shape[1]
     n = out.shape[0]
+    assert delta_scale is None or (delta_scale.dtype == torch.float32 and delta_scale.is_contiguous() and delta_scale.numel() == H)
     assert resid.dtype == torch.float32 and weight.dtype == torch.float32 and weight.numel() == H
     assert out.shape[1] == H and out.is_contiguous() and resid.is_contiguous()
     parts, stride, dcode = 1, 0, dtype_code(out.dtype)
@@ -482,7 +496,8 @@ def rmsnorm(out: torch.Tensor, resid: torch.Tensor, delta, weight: torch.Tensor,
     else:
         assert n == resid.shape[0]
     _check(core().le_rmsnorm(_ptr(out), dtype_code(out.dtype), _ptr(resid), _ptr(delta), dcode, parts, stride,
-                             _ptr(weight), _ptr(rows), float(eps), n, H, int(groups), _stream()), "le_rmsnorm")
+                             _ptr(weight), _ptr(rows), float(eps), n, H, int(groups), _ptr(delta_scale), _stream()),
+           "le_rmsnorm")
 
 
 def rmsnorm_taps_applies(hidden: int, groups: int) -> bool:
@@ -805,9 +820,12 @@ def _head_scale(head_scale, num_heads):
 
 
 def attention_generic(out, q, q_stride, k_cache, v_cache, block_table, cu_q, ctx_before, tile_request, tile_q0,
-                      num_tiles, num_heads, num_kv_heads, head_dim, page_size, reach, scale, status, head_scale=None) -> None:
+                      num_tiles, num_heads, num_kv_heads, head_dim, page_size, reach, scale, status, head_scale=None,
+                      keep_first: int = 0, softcap: float = 0.0) -> None:
     """``reach``: see reach_code.  ``head_scale`` (float32 [num_heads] or None):
-    one more factor per query head on its scores."""
+    one more factor per query head on its scores.  ``keep_first`` n: the keys
+    at positions below n stay visible behind a window.  ``softcap`` c > 0: a
+    score s becomes c * tanh(s / c)."""
     _need_cuda(out, q, k_cache, v_cache, block_table)
     lib = attention_lib(head_dim)
     assert out.is_contiguous() and out.shape[1] == num_heads * head_dim
@@ -816,7 +834,8 @@ def attention_generic(out, q, q_stride, k_cache, v_cache, block_table, cu_q, ctx
                                     dtype_code(out.dtype), _ptr(block_table), block_table.shape[1], _ptr(cu_q),
                                     _ptr(ctx_before), _ptr(tile_request), _ptr(tile_q0), num_tiles, num_heads,
                                     num_kv_heads, page_size, k_cache.shape[0], int(reach or 0), float(scale),
-                                    _head_scale(head_scale, num_heads), _ptr(status), _stream()), "le_attention_generic", lib)
+                                    _head_scale(head_scale, num_heads), int(keep_first), float(softcap), _ptr(status),
+                                    _stream()), "le_attention_generic", lib)
 
 
 def attention_mma_available(head_dim: int) -> bool:
@@ -827,9 +846,9 @@ def attention_mma_available(head_dim: int) -> bool:
 
 def attention_prefill_bf16(out, q, q_stride, k_cache, v_cache, block_table, cu_q, ctx_before, tile_request, tile_q0,
                            num_tiles, num_heads, num_kv_heads, head_dim, page_size, reach, scale, status,
-                           head_scale=None) -> None:
+                           head_scale=None, keep_first: int = 0, softcap: float = 0.0) -> None:
     """Tensor-core attention for requests that bring several tokens; the tiles
-    list 128 query tokens each."""
+    list 128 query tokens each.  ``keep_first``, ``softcap``: as attention_generic."""
     _need_cuda(out, q, k_cache, v_cache, block_table)
     lib = attention_lib(head_dim)
     assert out.dtype == torch.bfloat16 and out.is_contiguous() and out.shape[1] == num_heads * head_dim
@@ -838,7 +857,8 @@ def attention_prefill_bf16(out, q, q_stride, k_cache, v_cache, block_table, cu_q
                                          _ptr(block_table), block_table.shape[1], _ptr(cu_q), _ptr(ctx_before),
                                          _ptr(tile_request), _ptr(tile_q0), num_tiles, num_heads, num_kv_heads,
                                          page_size, k_cache.shape[0], int(reach or 0), float(scale),
-                                         _head_scale(head_scale, num_heads), _ptr(status), _stream()),
+                                         _head_scale(head_scale, num_heads), int(keep_first), float(softcap), _ptr(status),
+                                         _stream()),
            "le_attention_prefill_bf16", lib)
 
 
@@ -895,8 +915,9 @@ def attention_decode_resident_blocks(head_dim: int, num_splits: int, small: bool
 
 def attention_decode_bf16(out, scratch, q, q_stride, k_cache, v_cache, block_table, cu_q, ctx_before, requests,
                           num_requests, num_heads, num_kv_heads, head_dim, page_size, reach, scale, num_splits,
-                          status, small_form=None, head_scale=None) -> None:
-    """Split-key tensor-core attention for requests that bring one token.
+                          status, small_form=None, head_scale=None, keep_first: int = 0, softcap: float = 0.0) -> None:
+    """Split-key tensor-core attention for requests that bring one token
+    (``keep_first``, ``softcap``: as attention_generic).
     ``scratch``: float32, attention_decode_scratch_floats(...) elements.
     ``small_form``: None lets the launcher choose between the kernel's usual
     form and the one with 16-key tiles by the number of blocks; a caller that
@@ -913,7 +934,8 @@ def attention_decode_bf16(out, scratch, q, q_stride, k_cache, v_cache, block_tab
                                              _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(cu_q),
                                              _ptr(ctx_before), _ptr(requests), num_requests, num_heads, num_kv_heads,
                                              page_size, k_cache.shape[0], int(reach or 0), float(scale),
-                                             _head_scale(head_scale, num_heads), num_splits, form, _ptr(status), _stream()),
+                                             _head_scale(head_scale, num_heads), int(keep_first), float(softcap), num_splits,
+                                             form, _ptr(status), _stream()),
            "le_attention_decode_bf16", lib,
            launches=2 if num_splits > 1 else 1)       # the attention kernel and the merge
 
@@ -1072,10 +1094,14 @@ def moe_max_tiles(pairs: int, experts: int, wide: bool = False) -> int:
     return pairs // moe_tile_rows(wide) + min(experts, pairs)
 
 
-def moe_route(ids, weights, gate, h, w_router, b_router, w_gate, top: int, scratch=None) -> None:
+MOE_SOFTMAX_CHOSEN, MOE_SIGMOID = 0, 1
+
+
+def moe_route(ids, weights, gate, h, w_router, b_router, w_gate, top: int, scratch=None, scoring: int = MOE_SOFTMAX_CHOSEN) -> None:
     """Per row of ``h``: router logits W h + b in 32 bits, the ``top`` largest
     (``ids`` int32 [T, top], best first), softmax over the chosen logits
-    (``weights`` float32 [T, top]); with ``w_gate`` (float32 [W]) also
+    (``weights`` float32 [T, top]; ``scoring`` MOE_SIGMOID: each chosen
+    logit's own sigmoid instead, not renormalized); with ``w_gate`` (float32 [W]) also
     ``gate`` [T] = sigmoid(w_gate . h).  ``scratch``: float32, T * (experts +
     1) elements, for the logits (made here when not given: a caller whose
     steps are captured passes its own)."""
@@ -1092,7 +1118,8 @@ def moe_route(ids, weights, gate, h, w_router, b_router, w_gate, top: int, scrat
         scratch = torch.empty(T * (E + 1), dtype=torch.float32, device=h.device)
     assert scratch.dtype == torch.float32 and scratch.is_contiguous() and scratch.numel() >= T * (E + 1)
     _check(core().le_moe_route(_ptr(h), h.stride(0), dtype_code(h.dtype), _ptr(w_router), _ptr(b_router), _ptr(w_gate),
-                               _ptr(scratch), _ptr(ids), _ptr(weights), _ptr(gate), T, W, E, top, _stream()), "le_moe_route",
+                               _ptr(scratch), _ptr(ids), _ptr(weights), _ptr(gate), T, W, E, top, int(scoring), _stream()),
+           "le_moe_route",
            launches=2)
 
 
@@ -1116,22 +1143,26 @@ def moe_group(ids, experts: int, slot_pair, tiles, meta, wide: bool = False, pad
                                _ptr(tiles[2]), _ptr(meta), _stream()), "le_moe_group")
 
 
-def moe_gather(out, x, slot_pair, meta, src_div: int, wide: bool = True) -> None:
+def moe_gather(out, x, slot_pair, meta, src_div: int, wide: bool = True, pair_weight=None) -> None:
     """out[slot] = x[slot_pair[slot] // src_div] for the slots of the first
-    meta[0] row tiles (zeros where a slot stands for no pair)."""
-    _need_cuda(out, x, slot_pair, meta)
+    meta[0] row tiles (zeros where a slot stands for no pair); with
+    ``pair_weight`` (float32 [pairs]) the row times its pair's weight."""
+    _need_cuda(out, x, slot_pair, meta, pair_weight)
+    assert pair_weight is None or (pair_weight.dtype == torch.float32 and pair_weight.is_contiguous())
     assert out.dtype == x.dtype and out.is_contiguous() and x.stride(1) == 1 and out.shape[1] == x.shape[1]
     assert slot_pair.numel() >= out.shape[0]
     _check(core().le_moe_gather(_ptr(out), _ptr(x), x.stride(0), dtype_code(x.dtype), _ptr(slot_pair), int(src_div),
-                                moe_tile_rows(wide), _ptr(meta), out.shape[0], x.shape[1], _stream()), "le_moe_gather")
+                                moe_tile_rows(wide), _ptr(meta), out.shape[0], x.shape[1], _ptr(pair_weight), _stream()),
+           "le_moe_gather")
 
 
 def moe_combine_sorted(out, y, pair_slot, share, top: int, shared_out=None, gate=None) -> None:
-    """out[t] = sum_j share[t, j] * y[pair_slot[t * top + j]] (+ gate[t] * shared_out[t])."""
+    """out[t] = sum_j share[t, j] * y[pair_slot[t * top + j]] (+ gate[t] * shared_out[t]); ``share`` None: plain sum."""
     _need_cuda(out, y, pair_slot, share, shared_out, gate)
     T, W = out.shape
-    assert y.is_contiguous() and y.shape[1] == W and out.is_contiguous() and share.dtype == torch.float32
-    assert share.is_contiguous() and share.numel() == T * top and pair_slot.dtype == torch.int32 and pair_slot.numel() >= T * top
+    assert y.is_contiguous() and y.shape[1] == W and out.is_contiguous()
+    assert share is None or (share.dtype == torch.float32 and share.is_contiguous() and share.numel() == T * top)
+    assert pair_slot.dtype == torch.int32 and pair_slot.numel() >= T * top
     assert shared_out is None or (shared_out.dtype == out.dtype and shared_out.is_contiguous() and shared_out.shape == out.shape)
     _check(core().le_moe_combine_sorted(_ptr(out), dtype_code(out.dtype), _ptr(y), dtype_code(y.dtype), _ptr(pair_slot),
                                         _ptr(share), _ptr(shared_out), _ptr(gate), T, W, top, _stream()),
@@ -1163,7 +1194,9 @@ def moe_grouped(out, a, w, slot_pair, tiles, meta, max_tiles: int, src_div: int,
     """The product of every sorted slot's row with its expert's matrix
     ``w`` [experts, N (2 F when gated), K].  Input row of a slot: row pair //
     src_div of ``a`` (``src_div`` 0: row slot).  Output row: the slot, or with
-    ``scatter`` the pair, times ``pair_weight[pair]`` where given.  bfloat16
+    ``scatter`` the pair, times ``pair_weight[pair]`` where given (in the
+    gated form the weight multiplies both products before the activation: the
+    weight on the expert's input).  bfloat16
     with rows in 16-byte pieces: tensor cores (``wide``: the tiles moe_group
     made are the wide ones); else the FP32 pipes."""
     _need_cuda(out, a, w, slot_pair, tiles, meta, pair_weight)
@@ -1191,13 +1224,15 @@ def moe_combine(out, y, top: int, shared_out=None, gate=None) -> None:
 
 # -------------------------------------------------------------------------- convolution with activation, delta rule
 def short_conv_general(out, h, w_taps, state, state_slots, cu_q, tile_request, tile_q0, num_tiles, add_input: bool,
-                       silu: bool) -> None:
-    """short_conv() in its general form: ``h`` may be the first columns of
-    wider rows (any row stride); ``add_input`` False leaves the token's own
+                       silu: bool, bias=None) -> None:
+    """short_conv() in its general form: ``h`` may be a column range of wider
+    rows (any row stride); ``add_input`` False leaves the token's own
     input out of the sum (a plain causal convolution whose last tap is the
-    current token's); ``silu`` puts silu over the sum."""
-    _need_cuda(out, h, w_taps, state, state_slots, cu_q)
+    current token's); ``silu`` puts silu over the sum; ``bias`` (float32
+    [channels]) is added to the sum before it."""
+    _need_cuda(out, h, w_taps, state, state_slots, cu_q, bias)
     T, C = h.shape
+    assert bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == C)
     taps = w_taps.shape[0]
     assert out.shape == h.shape and out.dtype == h.dtype and out.is_contiguous() and h.stride(1) == 1
     assert w_taps.dtype == torch.float32 and w_taps.is_contiguous() and w_taps.shape[1] == C
@@ -1209,7 +1244,8 @@ def short_conv_general(out, h, w_taps, state, state_slots, cu_q, tile_request, t
     _check(core().le_short_conv_general(_ptr(out), _ptr(h), h.stride(0), dtype_code(h.dtype), _ptr(w_taps),
                                         _ptr(state) if taps > 1 else None, rows, _ptr(state_slots), _ptr(cu_q),
                                         _ptr(tile_request), _ptr(tile_q0), num_tiles, SHORT_CONV_TILE, C, taps,
-                                        1 if add_input else 0, 1 if silu else 0, _stream()), "le_short_conv_general")
+                                        1 if add_input else 0, 1 if silu else 0, _ptr(bias), _stream()),
+           "le_short_conv_general")
 
 
 GATED_DELTA_MAX_DIM = 1024
@@ -1248,17 +1284,21 @@ def gated_delta_scan(out, qkv, q_col, k_col, v_col, proj, b_col, a_col, a_log, d
            "le_gated_delta_scan")
 
 
-def head_norm_gate(out, o, gate, weight, eps, heads, vdim) -> None:
+def head_norm_gate(out, o, gate, weight, eps, heads, vdim, sigmoid: bool = False, out_scale: float = 1.0) -> None:
     """out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight *
     silu(gate[t, h, :]); ``o`` float32, ``gate`` and ``out`` in the
-    activations' type (column ranges of wider rows are fine)."""
+    activations' type (column ranges of wider rows are fine).  ``weight``
+    holds ``vdim`` numbers shared by the heads, or ``heads * vdim``.
+    ``sigmoid``: the gate's sigmoid instead of its silu; ``out_scale``: one
+    more factor on the result."""
     _need_cuda(out, o, gate, weight)
     T = o.shape[0]
     assert o.dtype == torch.float32 and o.shape == (T, heads * vdim) and out.shape == o.shape and gate.shape == o.shape
     assert out.dtype == gate.dtype and o.stride(1) == 1 and out.stride(1) == 1 and gate.stride(1) == 1
-    assert weight.dtype == torch.float32 and weight.numel() == vdim and weight.is_contiguous()
+    assert weight.dtype == torch.float32 and weight.numel() in (vdim, heads * vdim) and weight.is_contiguous()
     _check(core().le_head_norm_gate(_ptr(out), out.stride(0), _ptr(o), o.stride(0), _ptr(gate), gate.stride(0),
-                                    dtype_code(out.dtype), _ptr(weight), float(eps), T, heads, vdim, _stream()),
+                                    dtype_code(out.dtype), _ptr(weight), float(eps), T, heads, vdim,
+                                    1 if weight.numel() != vdim else 0, 1 if sigmoid else 0, float(out_scale), _stream()),
            "le_head_norm_gate")
 
 
@@ -1384,3 +1424,116 @@ def stream_entry(resid, table, ids, vec, status) -> None:
     _check(core().le_stream_entry(_ptr(resid), _ptr(table), dtype_code(table.dtype) if table is not None else F32, _ptr(ids),
                                   table.shape[0] if table is not None else 0, _ptr(vec), T, W, _ptr(status), _stream()),
            "le_stream_entry")
+
+
+# -------------------------------------------------------------------------- gates, state-space scans, matrix memory
+def sigmoid_gate(out, x, gate, scale: float = 1.0) -> None:
+    """out = x * sigmoid(gate) * scale, entry by entry; all three [T, W] in
+    the activations' type, each a column range of wider rows if need be
+    (``out`` may be ``x``)."""
+    _need_cuda(out, x, gate)
+    T, W = x.shape
+    assert out.shape == x.shape == gate.shape and out.dtype == x.dtype == gate.dtype
+    assert out.stride(1) == 1 and x.stride(1) == 1 and gate.stride(1) == 1
+    _check(core().le_sigmoid_gate(_ptr(out), out.stride(0), _ptr(x), x.stride(0), _ptr(gate), gate.stride(0),
+                                  dtype_code(x.dtype), T, W, float(scale), _stream()), "le_sigmoid_gate")
+
+
+SSM_MAX_STATE = 512
+
+
+def ssm_scan(out, x, bc, b_col: int, c_col: int, dt, z, dt_bias, a_log, d_skip, state, state_slots, cu_q, num_requests: int,
+             n_state: int, rows_per_head: int, rows_per_group: int, per_row: bool, out_scale: float = 1.0) -> None:
+    """A diagonal state-space recurrence over the step's tokens, request by
+    request, from each request's state row and back into it.  Per row r
+    (channel) with N = ``n_state`` numbers of state, per token:
+        dt = softplus(dt_raw + dt_bias);  S <- exp(dt * A) S + dt * x_r * B;  y = S . C + D * x_r
+        out = y * silu(z_r) * out_scale        (``z`` None: no gate)
+    with A = -exp(a_log).  ``per_row`` False: dt, dt_bias, D and a_log have
+    one entry per head of ``rows_per_head`` rows; True: one per row, and
+    ``a_log`` is [rows, N].  ``bc``: rows that hold B [groups, N] at column
+    ``b_col`` and C at ``c_col``; the rows of a group (``rows_per_group``
+    consecutive ones) share them.  ``x``, ``bc``, ``dt``, ``z`` are column
+    ranges of rows in the activations' type; ``out`` that type or float32;
+    ``state`` float32 [state rows, rows, N]."""
+    _need_cuda(out, x, bc, dt, z, dt_bias, a_log, d_skip, state, state_slots, cu_q)
+    T, rows = x.shape
+    assert out.shape == (T, rows) and out.stride(1) == 1 and x.stride(1) == 1 and bc.stride(1) == 1 and dt.stride(1) == 1
+    assert x.dtype == bc.dtype == dt.dtype and (z is None or (z.dtype == x.dtype and z.stride(1) == 1 and z.shape == x.shape))
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (rows, n_state)
+    entries = rows if per_row else rows // rows_per_head
+    assert dt_bias.dtype == torch.float32 and dt_bias.numel() == entries and dt.shape[1] >= entries
+    assert a_log.dtype == torch.float32 and a_log.is_contiguous() and a_log.numel() == (rows * n_state if per_row else entries)
+    assert d_skip is None or (d_skip.dtype == torch.float32 and d_skip.numel() == entries)
+    _check(core().le_ssm_scan(_ptr(out), dtype_code(out.dtype), out.stride(0), _ptr(x), x.stride(0), _ptr(bc), bc.stride(0),
+                              int(b_col), int(c_col), _ptr(dt), dt.stride(0), _ptr(z), z.stride(0) if z is not None else 0,
+                              dtype_code(x.dtype), _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(state), state.shape[0],
+                              _ptr(state_slots), _ptr(cu_q), int(num_requests), rows, int(n_state), int(rows_per_head),
+                              int(rows_per_group), 1 if per_row else 0, float(out_scale), _stream()), "le_ssm_scan")
+
+
+def mlstm_rows(dim: int, vdim: int) -> int:
+    """The columns of a head's matrix memory that one block of ``mlstm_scan``
+    takes (a divisor of ``vdim``); the state's layout follows it."""
+    return int(core().le_mlstm_rows(int(dim), int(vdim)))
+
+
+def mlstm_state_shape(heads: int, dim: int, vdim: int) -> tuple:
+    """The shape of a request's state for ``mlstm_scan``: per head and block
+    the block's columns of S, its copy of n, and a row whose first entry is m."""
+    r = mlstm_rows(dim, vdim)
+    return (heads, vdim // r, r + 2, dim)
+
+
+def mlstm_scan(out, rows, q_col: int, k_col: int, v_col: int, i_col: int, f_col: int, i_bias, f_bias, state, state_slots, cu_q,
+               num_requests: int, heads: int, dim: int, vdim: int, cap: float, q_scale: float) -> None:
+    """The mLSTM's matrix memory over the step's tokens, request by request.
+    ``rows``: per token q, k [heads, dim], v [heads, vdim] and one gate
+    pre-activation per head for the input and the forget gate, at the given
+    columns.  With i = cap tanh((a_i + b_i) / cap), f = logsigmoid(cap
+    tanh((a_f + b_f) / cap)) and a running maximum m (from 0):
+        m' = max(f + m, i);  S <- e^(f + m - m') S + e^(i - m') k v^T;  n likewise with k
+        out = S^T (q * q_scale) / (max(|n . q * q_scale|, e^(-m')) + 1e-6)
+    ``out`` float32 [T, heads * vdim]; ``state`` float32 [state rows,
+    *mlstm_state_shape()]."""
+    _need_cuda(out, rows, i_bias, f_bias, state, state_slots, cu_q)
+    T = rows.shape[0]
+    assert out.dtype == torch.float32 and out.shape == (T, heads * vdim) and out.stride(1) == 1 and rows.stride(1) == 1
+    assert i_bias.dtype == torch.float32 and f_bias.dtype == torch.float32 and i_bias.numel() == heads and f_bias.numel() == heads
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == mlstm_state_shape(heads, dim, vdim)
+    _check(core().le_mlstm_scan(_ptr(out), out.stride(0), _ptr(rows), rows.stride(0), int(q_col), int(k_col), int(v_col),
+                                int(i_col), int(f_col), dtype_code(rows.dtype), _ptr(i_bias), _ptr(f_bias), _ptr(state),
+                                state.shape[0], _ptr(state_slots), _ptr(cu_q), int(num_requests), int(heads), int(dim), int(vdim),
+                                float(cap), float(q_scale), _stream()), "le_mlstm_scan")
+
+
+def rope_qknorm_store(rows, bias, w_q, w_k, eps, q_count, k_count, rates, rot, magnitude, k_cache, v_cache, positions,
+                      request_of_token, block_table, heads, kv_heads, head_dim, page_size, write_kv, status) -> None:
+    """Rows hold q [heads, head_dim] | k [kv_heads, head_dim] | v [kv_heads,
+    head_dim].  ``bias`` (float32, the rows' width, or None) is added; q as a
+    whole (and k as a whole) is divided by sqrt(sum of squares / ``q_count`` +
+    eps) and multiplied by ``w_q`` (``w_k``), float32, both None for no norm;
+    in every head of q and k entry i < rot / 2 turns with entry i + rot / 2 by
+    position * rates[i], cosine and sine times ``magnitude``.  Queries are
+    rewritten in place; keys and values go to the caches' pages when
+    ``write_kv``."""
+    _need_cuda(rows, bias, w_q, w_k, rates, k_cache, v_cache, positions, block_table)
+    T = rows.shape[0]
+    width = (heads + 2 * kv_heads) * head_dim
+    assert rows.stride(1) == 1 and rows.shape[1] >= width
+    assert bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == width)
+    assert (w_q is None) == (w_k is None)
+    assert w_q is None or (w_q.dtype == torch.float32 and w_q.numel() == heads * head_dim and w_k.dtype == torch.float32
+                           and w_k.numel() == kv_heads * head_dim and w_q.is_contiguous() and w_k.is_contiguous())
+    assert rates.dtype == torch.float32 and rates.is_contiguous() and rates.numel() >= rot // 2
+    pages = 0
+    if write_kv:
+        assert k_cache.dtype == rows.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+        assert tuple(k_cache.shape[1:]) == (kv_heads, page_size, head_dim) and v_cache.shape == k_cache.shape
+        pages = k_cache.shape[0]
+    _check(core().le_rope_qknorm_store(_ptr(rows), rows.stride(0), dtype_code(rows.dtype), _ptr(bias), _ptr(w_q), _ptr(w_k),
+                                       float(eps), int(q_count), int(k_count), _ptr(rates), int(rot), float(magnitude),
+                                       _ptr(k_cache) if write_kv else None, _ptr(v_cache) if write_kv else None,
+                                       _ptr(positions), _ptr(request_of_token), _ptr(block_table), block_table.shape[1], T,
+                                       heads, kv_heads, head_dim, page_size, pages, 1 if write_kv else 0, _ptr(status),
+                                       _stream()), "le_rope_qknorm_store")

@@ -22,7 +22,13 @@ What a description may choose beyond the reference's Llama layer:
 * ``position`` None: queries and keys are used as projected;
 * ``gate_name``: a tensor [nh, H]; head h's output is multiplied by
   sigmoid(gate_h . x) before the output projection (the gate's rows ride at
-  the end of the fused projection);
+  the end of the fused projection); with ``gate_per_entry`` the tensor is
+  [nh * value_dim, H] and every entry of the heads' outputs has a gate of
+  its own;
+* ``keep_first`` n (with a window): the keys at positions below n stay
+  visible to every later query, with their true positions; their pages are
+  never given back;
+* ``softcap`` c: a score s (after the scale) becomes c * tanh(s / c);
 * ``v_name`` None: there is no value projection, the values are the keys as
   projected (before any position encoding or norm of the keys); the position
   encoding then fills the value pool itself (it is built with
@@ -77,7 +83,8 @@ class AttentionMixer(Mixer):
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, position: PartSpec | None,
                  q_name: str, k_name: str, v_name: str | None, o_name: str, window: int | None = None,
                  chunk: int | None = None, scale: float | None = None, value_dim: int | None = None,
-                 head_scale_name: str | None = None, gate_name: str | None = None):
+                 head_scale_name: str | None = None, gate_name: str | None = None, gate_per_entry: bool = False,
+                 keep_first: int = 0, softcap: float | None = None):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads do not divide into {num_kv_heads} groups")
         self.qk_dim = int(head_dim)
@@ -94,7 +101,9 @@ class AttentionMixer(Mixer):
         if position is not None and self.head_dim != self.qk_dim and not getattr(self.position, "padded_heads_ok", False):
             raise ValueError(f"a position encoding needs a query/key size that is a multiple of 16 and not below the "
                              f"value size, got {head_dim} and {self.value_dim}")
-        if position is not None and gate_name:
+        if hasattr(self.position, "set_geometry"):
+            self.position.set_geometry(self.head_dim)
+        if position is not None and gate_name and not getattr(self.position, "takes_gate_columns", False):
             raise ValueError("an output gate beside a position encoding is not supported (the encoding's kernels take "
                              "the projection's rows without gate columns)")
         if not 16 <= self.head_dim <= attention_kernels.MAX_HEAD_DIM:
@@ -103,16 +112,26 @@ class AttentionMixer(Mixer):
         self.window = int(window) if window else None
         self.chunk = int(chunk) if chunk else None
         self.reach = ops.reach_code(self.window, self.chunk)
+        self.keep_first = int(keep_first or 0) if self.window else 0      # (without a window every key is visible anyway)
+        if self.keep_first < 0:
+            raise ValueError(f"keep_first must not be negative, got {keep_first}")
+        self.softcap = float(softcap) if softcap else 0.0
+        if self.softcap < 0:
+            raise ValueError(f"a cap on the scores must be positive, got {softcap}")
         self.scale = float(scale) if scale is not None else 1.0 / (self.qk_dim ** 0.5)
         self.names = (q_name, k_name, v_name, o_name)
         self.head_scale_name, self.gate_name = head_scale_name, gate_name
-        self.gate_rows = (self.num_heads + 7) // 8 * 8 if gate_name else 0      # rows of the projection stay 16-byte multiples
+        self.gate_per_entry = bool(gate_per_entry) and bool(gate_name)
+        # rows of the projection stay 16-byte multiples
+        self.gate_rows = 0
+        if gate_name:
+            self.gate_rows = self.num_heads * self.head_dim if self.gate_per_entry else (self.num_heads + 7) // 8 * 8
         self.w_qkv = self.w_o = self.head_scale = None
         self.head_scale_positive = True
         self.runtime = None
 
     def cache_need(self):
-        return KVNeed(self.num_kv_heads, self.head_dim, self.window, self.chunk)
+        return KVNeed(self.num_kv_heads, self.head_dim, self.window, self.chunk, keep_first=self.keep_first)
 
     def tile_sizes(self):
         return attention_kernels.tile_sizes()
@@ -121,7 +140,7 @@ class AttentionMixer(Mixer):
         if self.runtime is None or self.runtime.dtype != torch.bfloat16:
             return None                       # the float32 kernel takes every shape the same way
         return attention_kernels.decode_variant(fill, self.num_heads, self.num_kv_heads, self.head_dim, context_bound,
-                                                self.reach)
+                                                self.reach, keep_first=self.keep_first)
 
     def tensors(self):
         q, k, v, o = self.names
@@ -133,7 +152,7 @@ class AttentionMixer(Mixer):
         if self.head_scale_name:
             decls.append(TensorDecl(self.head_scale_name, (nh,), role="vector", init="ones_jitter"))
         if self.gate_name:
-            decls.append(TensorDecl(self.gate_name, (nh, H)))
+            decls.append(TensorDecl(self.gate_name, (nh * self.value_dim if self.gate_per_entry else nh, H)))
         return decls + (self.position.tensors() if self.position is not None else [])
 
     def bind(self, get, runtime):
@@ -142,7 +161,9 @@ class AttentionMixer(Mixer):
         rows = [pad_head_rows(get(q), nh, self.qk_dim, hd), pad_head_rows(get(k), nkv, self.qk_dim, hd)]
         if not self.values_are_keys:
             rows.append(pad_head_rows(get(v), nkv, self.value_dim, hd))
-        if self.gate_name:
+        if self.gate_name and self.gate_per_entry:
+            rows.append(pad_head_rows(get(self.gate_name), nh, self.value_dim, hd))
+        elif self.gate_name:
             gate = get(self.gate_name)
             pad = torch.zeros((self.gate_rows - nh, gate.shape[1]), dtype=gate.dtype, device=gate.device)
             rows += [gate, pad]
@@ -155,7 +176,22 @@ class AttentionMixer(Mixer):
             self.position.bind(get, runtime)
         attention_kernels.prepare(self.head_dim)
 
+    def inner_width(self) -> int:
+        """Columns of what the output projection reads (the heads as the kernels hold them)."""
+        return self.num_heads * self.head_dim
+
+    def output_weight(self):
+        return self.w_o
+
     def forward(self, x, ctx, cache):
+        return ops.linear_for_residual(self.forward_inner(x, ctx, cache), self.w_o, ctx.workspace, "mixer_out", ctx.status)
+
+    def forward_inner(self, x, ctx, cache, out=None, scale: float = 1.0):
+        """The heads' outputs, gated, before the output projection: [T, nh *
+        head_dim], into ``out`` where given (a column range of wider rows is
+        fine) and times ``scale``: for a caller that has its own use for
+        them.  Only a mixer with a gate per entry writes elsewhere than its
+        own buffer or scales."""
         rt = self.runtime
         nh, nkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
         T = x.shape[0]
@@ -173,7 +209,13 @@ class AttentionMixer(Mixer):
                              ctx.block_tables[cache.kv.group], nkv, hd, cache.kv.page_size, ctx.status)
         attn = ws.get("attn", (T, nh * hd), rt.dtype)
         attention_kernels.run(attn, qkv, ctx, cache.kv, nh, nkv, hd, self.reach, self.kernel_scale, self.head_scale,
-                              self.head_scale_positive)
+                              self.head_scale_positive, keep_first=self.keep_first, softcap=self.softcap)
+        if self.gate_per_entry:
+            target = out if out is not None else attn
+            ops.sigmoid_gate(target, attn, qkv[:, width:width + nh * hd], scale)
+            return target
+        if out is not None or scale != 1.0:
+            raise ValueError("only a mixer with a gate per entry hands its heads' outputs on elsewhere or scaled")
         if self.gate_rows:
             ops.head_gate(attn, qkv[:, width:width + nh], nh, hd)
-        return ops.linear_for_residual(attn, self.w_o, ws, "mixer_out", ctx.status)
+        return attn

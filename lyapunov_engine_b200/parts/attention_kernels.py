@@ -113,13 +113,14 @@ def decode_splits(num_requests: int, num_heads: int, num_kv_heads: int, context_
                                 small, ops.sm_count())
 
 
-def keys_bound(context_bound: int, reach: int) -> int:
-    """The most keys a decoded token reads: its context, or its window or chunk where that is shorter."""
-    return min(context_bound, abs(reach)) if reach else context_bound
+def keys_bound(context_bound: int, reach: int, keep_first: int = 0) -> int:
+    """The most keys a decoded token reads: its context, or its window or chunk
+    (and the first keys that stay visible behind it) where that is shorter."""
+    return min(context_bound, abs(reach) + int(keep_first)) if reach else context_bound
 
 
 def decode_variant(fill: int, num_heads: int, num_kv_heads: int, head_dim: int, context_bound: int, reach: int = 0,
-                   max_splits: int = DECODE_MAX_SPLITS):
+                   max_splits: int = DECODE_MAX_SPLITS, keep_first: int = 0):
     """The split count (and the kernel's form, where it is not the usual one)
     of a step in which ``fill`` of the one-token requests are real: dummy
     requests finish at once, so the real ones alone fill the waves (9 real
@@ -127,39 +128,50 @@ def decode_variant(fill: int, num_heads: int, num_kv_heads: int, head_dim: int, 
     if not SPLITS_BY_FILL or not ops.attention_mma_available(head_dim):
         return None
     fill = max(1, fill)
-    splits = min(max_splits, decode_splits(fill, num_heads, num_kv_heads, keys_bound(context_bound, reach), head_dim))
+    splits = min(max_splits, decode_splits(fill, num_heads, num_kv_heads, keys_bound(context_bound, reach, keep_first), head_dim))
     # (the kernel's form follows the real requests too)
     return (splits, "small") if decode_small_form(fill, num_heads, num_kv_heads, head_dim) else splits
 
 
 def run(out, qkv, ctx, kv, num_heads, num_kv_heads, head_dim, reach, scale, head_scale=None,
-        head_scale_positive: bool = True, max_splits: int = DECODE_MAX_SPLITS) -> None:
+        head_scale_positive: bool = True, max_splits: int = DECODE_MAX_SPLITS, keep_first: int = 0,
+        softcap: float = 0.0) -> None:
     """``reach``: which keys a query sees (ops.reach_code); ``head_scale``: one
     more factor per query head on its scores (float32 [num_heads]) or None.
     The tcgen05 kernel folds that factor into its exponent's scale and so takes
-    positive factors only; the others apply it to the scores themselves."""
+    positive factors only; the others apply it to the scores themselves.
+    ``keep_first`` n: the keys at positions below n stay visible behind a
+    window; ``softcap`` c > 0: a score s becomes c * tanh(s / c).  The tcgen05
+    kernel has neither (its keys are one unbroken run and its scores stay raw
+    products until the exponent): prompts of such a mixer take the mma.sync kernel."""
     table = ctx.block_tables[kv.group]
     window = reach
     if out.dtype == torch.bfloat16 and ops.attention_mma_available(head_dim):
         req, q0, n_tiles, n_multi = ctx.tiles[PREFILL_TILE]
         if n_multi:
-            prefill = (ops.attention_prefill_tc_bf16
-                       if USE_TC_ATTENTION and head_scale_positive and ops.attention_tc_available(head_dim, kv.page_size)
-                       else ops.attention_prefill_bf16)
-            prefill(out, qkv, qkv.stride(0), kv.k, kv.v, table, ctx.cu_q, ctx.ctx_before, req, q0, n_multi, num_heads,
-                    num_kv_heads, head_dim, kv.page_size, window, scale, ctx.status, head_scale=head_scale)
+            if (USE_TC_ATTENTION and head_scale_positive and not keep_first and not softcap
+                    and ops.attention_tc_available(head_dim, kv.page_size)):
+                ops.attention_prefill_tc_bf16(out, qkv, qkv.stride(0), kv.k, kv.v, table, ctx.cu_q, ctx.ctx_before, req, q0,
+                                              n_multi, num_heads, num_kv_heads, head_dim, kv.page_size, window, scale,
+                                              ctx.status, head_scale=head_scale)
+            else:
+                ops.attention_prefill_bf16(out, qkv, qkv.stride(0), kv.k, kv.v, table, ctx.cu_q, ctx.ctx_before, req, q0,
+                                           n_multi, num_heads, num_kv_heads, head_dim, kv.page_size, window, scale,
+                                           ctx.status, head_scale=head_scale, keep_first=keep_first, softcap=softcap)
         if ctx.num_decode:
             real = min(ctx.decode_fill, ctx.num_decode) if SPLITS_BY_FILL else 0     # dummy requests finish at once
             splits = min(max_splits, decode_splits(real or ctx.num_decode, num_heads, num_kv_heads,
-                                                   keys_bound(ctx.context_bound, reach), head_dim))
+                                                   keys_bound(ctx.context_bound, reach, keep_first), head_dim))
             small = decode_small_form(real or ctx.num_decode, num_heads, num_kv_heads, head_dim)
             floats = ops.attention_decode_scratch_floats(head_dim, ctx.num_decode, num_heads, splits)
             scratch = ctx.workspace.get("attention_scratch", (floats,), torch.float32) if floats else None
             requests = None if ctx.num_decode == ctx.num_requests else ctx.decode_requests
             ops.attention_decode_bf16(out, scratch, qkv, qkv.stride(0), kv.k, kv.v, table, ctx.cu_q, ctx.ctx_before,
                                       requests, ctx.num_decode, num_heads, num_kv_heads, head_dim, kv.page_size,
-                                      window, scale, splits, ctx.status, small_form=small, head_scale=head_scale)
+                                      window, scale, splits, ctx.status, small_form=small, head_scale=head_scale,
+                                      keep_first=keep_first, softcap=softcap)
         return
     req, q0, n_tiles, _ = ctx.tiles[GENERIC_TILE]
     ops.attention_generic(out, qkv, qkv.stride(0), kv.k, kv.v, table, ctx.cu_q, ctx.ctx_before, req, q0, n_tiles,
-                          num_heads, num_kv_heads, head_dim, kv.page_size, window, scale, ctx.status, head_scale=head_scale)
+                          num_heads, num_kv_heads, head_dim, kv.page_size, window, scale, ctx.status, head_scale=head_scale,
+                          keep_first=keep_first, softcap=softcap)

@@ -131,12 +131,15 @@ class KVNeed:
     only; ``chunk`` c: a query reads the keys of its own chunk of c positions
     only (chunks counted from position 0); neither: every key is kept.
     ``values`` False: one pool serves as keys and as values (a mixer that
-    attends over one latent vector per token)."""
+    attends over one latent vector per token).  ``keep_first`` n (with a
+    window): the keys at positions below n stay visible to every later query,
+    so the pages that hold them are never given back while the request lives."""
     num_kv_heads: int
     head_dim: int
     window: int | None = None
     chunk: int | None = None
     values: bool = True
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)
@@ -245,6 +248,16 @@ class NormedAddend:
         self.weight, self.eps = weight, float(eps)
 
 
+class ScaledAddend:
+    """How a pending output enters the stream when every column has a learned
+    factor (a layer scale): resid += weight * pending (weight [W], 32-bit),
+    applied by the norm that reads the stream, in its own kernel."""
+    __slots__ = ("weight",)
+
+    def __init__(self, weight):
+        self.weight = weight
+
+
 class Block(Part):
     mixer: Mixer
 
@@ -269,7 +282,8 @@ class ResidualStream:
     stream; ``update`` says how ``pending`` enters: None: resid += pending;
     a ``StreamLink`` whose ``mix`` [copies, copies] and ``post`` [copies]
     give copy j <- sum_s mix[s, j] copy_s + post[j] * pending; a
-    ``NormedAddend``: resid += pending normed with a weight."""
+    ``NormedAddend``: resid += pending normed with a weight; a
+    ``ScaledAddend``: resid += weight * pending."""
     __slots__ = ("resid", "pending", "update", "copies")
 
     def __init__(self, resid, pending=None):

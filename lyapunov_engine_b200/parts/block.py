@@ -9,20 +9,26 @@ leaves its feed-forward output ``pending`` and the next norm (of the next
 block, or the final one) adds it.  Two options: ``mixer_input``, an input
 filter between the first norm and the mixer (h = filter(norm1(h)) is what the
 mixer reads), and a block without a feed-forward (``feed_forward`` None: only
-the first line above).
+the first line above).  With layer scales (``mixer_scale_name``,
+``feed_forward_scale_name``: a learned factor per column, 32-bit) a
+sub-layer's output enters the stream times its factor, h = h + s1 *
+mixer(norm1(h)); h = h + s2 * feed_forward(norm2(h)); the norm's kernel that
+adds the output multiplies it.
 
 "parallel": both sub-layers read the same stream (see ``ParallelBlock``).
 """
 from __future__ import annotations
 
 from .. import ops
-from .base import BLOCKS, FEED_FORWARDS, INPUT_FILTERS, MIXERS, NORMS, STREAM_INPUTS, Block, PartSpec, register_block
+from .base import (BLOCKS, FEED_FORWARDS, INPUT_FILTERS, MIXERS, NORMS, STREAM_INPUTS, Block, PartSpec, ScaledAddend,
+                   TensorDecl, register_block)
 
 
 @register_block("prenorm")
 class PreNormBlock(Block):
     def __init__(self, mixer: PartSpec, feed_forward: PartSpec | None, mixer_norm: PartSpec,
-                 feed_forward_norm: PartSpec | None, mixer_input: PartSpec | None = None):
+                 feed_forward_norm: PartSpec | None, mixer_input: PartSpec | None = None,
+                 mixer_scale_name: str | None = None, feed_forward_scale_name: str | None = None):
         if (feed_forward is None) != (feed_forward_norm is None):
             raise ValueError("a block has a feed-forward and its norm, or neither")
         self.mixer = MIXERS.build(mixer)
@@ -30,6 +36,11 @@ class PreNormBlock(Block):
         self.mixer_norm = NORMS.build(mixer_norm)
         self.feed_forward_norm = NORMS.build(feed_forward_norm) if feed_forward_norm is not None else None
         self.mixer_input = INPUT_FILTERS.build(mixer_input) if mixer_input is not None else None
+        self.mixer_scale_name = mixer_scale_name
+        self.feed_forward_scale_name = feed_forward_scale_name if feed_forward is not None else None
+        self.mixer_scale = self.feed_forward_scale = None
+        if (mixer_scale_name or self.feed_forward_scale_name) and mixer_input is not None:
+            raise ValueError("layer scales beside an input filter are not supported")
 
     def parts(self):
         return [p for p in (self.mixer_norm, self.mixer_input, self.mixer, self.feed_forward_norm, self.feed_forward)
@@ -46,13 +57,32 @@ class PreNormBlock(Block):
         return list(self.mixer.tile_sizes()) + (self.mixer_input.tile_sizes() if self.mixer_input is not None else [])
 
     def tensors(self):
-        return [d for p in self.parts() for d in p.tensors()]
+        width = getattr(self.mixer_norm, "hidden_size", None)
+        scales = [TensorDecl(name, (width,), role="vector", init="ones_jitter")
+                  for name in (self.mixer_scale_name, self.feed_forward_scale_name) if name]
+        return [d for p in self.parts() for d in p.tensors()] + scales
 
     def bind(self, get, runtime):
         for p in self.parts():
             p.bind(get, runtime)
+        self.mixer_scale = get(self.mixer_scale_name).contiguous() if self.mixer_scale_name else None
+        self.feed_forward_scale = get(self.feed_forward_scale_name).contiguous() if self.feed_forward_scale_name else None
+
+    def _leave(self, stream, output, scale) -> None:
+        stream.pending = output
+        stream.update = ScaledAddend(scale) if scale is not None else None
 
     def forward(self, stream, ctx, cache) -> None:
+        if self.mixer_scale is not None or self.feed_forward_scale is not None or isinstance(stream.update, ScaledAddend):
+            # (a pending output with a factor per column: the norms' kernels multiply as they add)
+            n = self.mixer_norm.apply_stream(stream, workspace=ctx.workspace)
+            a = self.mixer.forward(n, ctx, cache)
+            if self.feed_forward is None:
+                self._leave(stream, a, self.mixer_scale)
+                return
+            n = self.feed_forward_norm.apply(stream.resid, a, workspace=ctx.workspace, delta_scale=self.mixer_scale)
+            self._leave(stream, self.feed_forward.forward(n, ctx), self.feed_forward_scale)
+            return
         n = None
         if self.mixer_input is not None:
             # an input filter may know how to run the norm before it in its own kernel

@@ -17,8 +17,10 @@ from .base import Part, TensorDecl, register_embedding, register_head
 
 @register_embedding("token_embedding")
 class TokenEmbedding(Part):
-    def __init__(self, vocab_size: int, hidden_size: int, weight_name: str):
+    def __init__(self, vocab_size: int, hidden_size: int, weight_name: str, scale: float = 1.0):
+        """``scale``: h0[t] = E[id_t] * scale, the product taken in 32 bits."""
         self.vocab_size, self.hidden_size, self.weight_name = int(vocab_size), int(hidden_size), weight_name
+        self.scale = float(scale)
         self.weight = None
         self.runtime = None
 
@@ -31,7 +33,7 @@ class TokenEmbedding(Part):
 
     def forward(self, ctx):
         resid = ctx.workspace.get("resid", (ctx.num_tokens, self.hidden_size), torch.float32)
-        ops.embed(resid, self.weight, ctx.token_ids, ctx.status)
+        ops.embed(resid, self.weight, ctx.token_ids, ctx.status, self.scale)
         return resid
 
 

@@ -9,7 +9,7 @@ are bare parameters of the decoder layer (python/lyapunov_engine/models/llama.py
 from __future__ import annotations
 
 from .. import ops
-from .base import Norm, NormedAddend, TensorDecl, register_norm
+from .base import Norm, NormedAddend, ScaledAddend, TensorDecl, register_norm
 
 
 @register_norm("rmsnorm")
@@ -44,14 +44,21 @@ class RMSNorm(Norm):
             self.weight = (self.weight + self.offset).contiguous()
         self.runtime = runtime
 
-    def apply(self, resid, delta=None, rows=None, workspace=None, key="normed"):
+    def apply(self, resid, delta=None, rows=None, workspace=None, key="normed", delta_scale=None):
+        """``delta_scale`` (32-bit [hidden]): the delta enters the stream times it."""
         n = resid.shape[0] if rows is None else rows.shape[0]
         ws = workspace or self.runtime.workspace
         out = ws.get(key, (n, self.hidden_size), self.runtime.dtype)
-        ops.rmsnorm(out, resid, delta, self.weight, self.eps, rows, groups=self.groups)
+        ops.rmsnorm(out, resid, delta, self.weight, self.eps, rows, groups=self.groups, delta_scale=delta_scale)
         return out
 
     def apply_stream(self, stream, read=None, rows=None, workspace=None, key="normed"):
+        if isinstance(stream.update, ScaledAddend) and stream.copies == 1 and read is None:
+            out = self.apply(stream.resid, stream.pending, rows=rows, workspace=workspace, key=key,
+                             delta_scale=stream.update.weight if stream.pending is not None else None)
+            if rows is None:
+                stream.pending = stream.update = None
+            return out
         if not isinstance(stream.update, NormedAddend):
             return super().apply_stream(stream, read, rows, workspace, key)
         return self.apply_pair(stream, None, rows=rows, workspace=workspace, keys=(key, None))[0]

@@ -145,3 +145,116 @@ class RotaryPairsEncoding(PositionEncoding):
             # (values of their own: stored as projected; the store kernel writes two pools, both are the values' here)
             ops.kv_store(qkv, (nh + nkv) * hd, (nh + nkv) * hd, kv.v, kv.v, ctx.positions, ctx.request_of_token,
                          ctx.block_tables[kv.group], nkv, hd, kv.page_size, ctx.status)
+
+
+def ramped_rates(rot: int, base: float, scaling: dict | None) -> tuple[torch.Tensor, float]:
+    """(rates f_i for i < rot / 2, the factor on cosines and sines).  Plain:
+    f_i = base^(-2i / rot) and 1.  With ``scaling`` = {factor, original, fast,
+    slow} (the blend known as YaRN): the pair index at which a rate makes t
+    turns over ``original`` positions is d(t) = rot ln(original / (2 pi t)) /
+    (2 ln base); between lo = max(floor(d(fast)), 0) and hi = min(ceil(d(slow)),
+    rot - 1) a ramp r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) blends
+    f_i (fast pairs, r = 0) into f_i / factor (slow pairs, r = 1), and cosines
+    and sines are multiplied by 0.1 ln(factor) + 1.  Made in 64 bits, kept as
+    float32."""
+    i = torch.arange(max(rot, 2) // 2, dtype=torch.float64)
+    rates = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / max(rot, 2))
+    if not scaling:
+        return rates.to(torch.float32), 1.0
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+
+    def pair_of(turns: float) -> float:
+        return rot * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+    lo = max(math.floor(pair_of(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(pair_of(float(scaling["slow"]))), rot - 1)
+    ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    rates = rates / factor * ramp + rates * (1.0 - ramp)
+    return rates.to(torch.float32), 0.1 * math.log(factor) + 1.0
+
+
+@register_position_encoding("rotary_normed")
+class NormedRotaryEncoding(PositionEncoding):
+    """Rotary positions in the rotate-half layout (entry i < rot / 2 of a head
+    turns with entry i + rot / 2), with what a projection may want before the
+    turn, all in one kernel with the cache write: biases on q, k and v
+    (``bias_names``), and a norm over the whole of q and over the whole of k
+    (not per head): x / sqrt(mean(x^2) + eps) * w with ``q_norm_name`` [heads
+    * head_dim] and ``k_norm_name`` [kv_heads * head_dim].  ``scaling``: see
+    ramped_rates.  No table: angle, cosine and sine are made in 32 bits from
+    the step's own positions.  ``head_dim`` is the real size of queries and
+    keys (``value_dim`` of values); the heads the kernels see may be padded
+    with zeros behind it (``set_geometry``)."""
+    padded_heads_ok = True
+    takes_gate_columns = True       # the kernel walks rows by their stride: columns behind q | k | v are left alone
+
+    def __init__(self, num_heads: int, num_kv_heads: int, head_dim: int, rot: int, base: float, scaling: dict | None = None,
+                 norm_eps: float | None = None, q_norm_name: str | None = None, k_norm_name: str | None = None,
+                 bias_names: tuple | None = None, value_dim: int | None = None):
+        self.num_heads, self.num_kv_heads, self.head_dim = int(num_heads), int(num_kv_heads), int(head_dim)
+        self.value_dim = int(value_dim) if value_dim else self.head_dim
+        self.rot, self.base = int(rot), float(base)
+        if self.rot % 2 or not 0 <= self.rot <= self.head_dim:
+            raise ValueError(f"rotary width {rot} must be even and at most the head size {head_dim}")
+        if (q_norm_name is None) != (k_norm_name is None):
+            raise ValueError("queries and keys are normed both or neither")
+        if q_norm_name is not None and norm_eps is None:
+            raise ValueError("a norm over the projections needs its eps")
+        self.scaling = dict(scaling) if scaling else None
+        self.norm_eps = float(norm_eps) if norm_eps is not None else 0.0
+        self.q_norm_name, self.k_norm_name = q_norm_name, k_norm_name
+        self.bias_names = tuple(bias_names) if bias_names else None
+        self.padded = self.head_dim
+        self.rates = self.bias = self.w_q = self.w_k = None
+        self.magnitude = 1.0
+
+    def set_geometry(self, padded_head_dim: int) -> None:
+        """The head size of kernels and pages (at least the real sizes)."""
+        self.padded = int(padded_head_dim)
+
+    def tensors(self):
+        from .base import TensorDecl
+        nh, nkv, d, e = self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim
+        decls = []
+        if self.q_norm_name:
+            decls += [TensorDecl(self.q_norm_name, (nh * d,), role="vector", init="ones_jitter"),
+                      TensorDecl(self.k_norm_name, (nkv * d,), role="vector", init="ones_jitter")]
+        if self.bias_names:
+            qb, kb, vb = self.bias_names
+            decls += [TensorDecl(qb, (nh * d,), role="vector", init="taps"), TensorDecl(kb, (nkv * d,), role="vector", init="taps"),
+                      TensorDecl(vb, (nkv * e,), role="vector", init="taps")]
+        return decls
+
+    def _padded(self, t: torch.Tensor, heads: int, size: int) -> torch.Tensor:
+        if size == self.padded:
+            return t.reshape(-1).contiguous()
+        out = torch.zeros((heads, self.padded), dtype=t.dtype, device=t.device)
+        out[:, :size] = t.view(heads, size)
+        return out.view(-1)
+
+    def bind(self, get, runtime):
+        key = ("rotary_normed", self.rot, self.base, repr(self.scaling))
+        found = runtime.shared.get(key)
+        if found is None:
+            rates, magnitude = ramped_rates(self.rot, self.base, self.scaling)
+            found = runtime.shared[key] = (rates.to(runtime.device).contiguous(), magnitude)
+        self.rates, self.magnitude = found
+        nh, nkv, d, e = self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim
+        if self.q_norm_name:
+            self.w_q = self._padded(get(self.q_norm_name).to(torch.float32), nh, d)
+            self.w_k = self._padded(get(self.k_norm_name).to(torch.float32), nkv, d)
+        if self.bias_names:
+            qb, kb, vb = (get(n).to(torch.float32) for n in self.bias_names)
+            self.bias = torch.cat([self._padded(qb, nh, d), self._padded(kb, nkv, d), self._padded(vb, nkv, e)]).contiguous()
+
+    def encode_and_store(self, qkv, geometry, ctx, kv, write: bool) -> None:
+        nh, nkv, hd = geometry
+        if (nh, nkv, hd) != (self.num_heads, self.num_kv_heads, self.padded):
+            raise ValueError(f"the encoding was built for {self.num_heads} + {self.num_kv_heads} heads of {self.padded}, "
+                             f"the mixer brings {nh} + {nkv} of {hd}")
+        write = write and kv is not None
+        ops.rope_qknorm_store(qkv, self.bias, self.w_q, self.w_k, self.norm_eps, nh * self.head_dim, nkv * self.head_dim,
+                              self.rates, self.rot, self.magnitude, kv.k if write else None, kv.v if write else None,
+                              ctx.positions, ctx.request_of_token,
+                              ctx.block_tables[kv.group] if kv is not None else ctx.block_tables[0], nh, nkv, hd,
+                              kv.page_size if kv is not None else 1, write, ctx.status)

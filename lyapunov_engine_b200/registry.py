@@ -51,12 +51,14 @@ def _register_builtin() -> None:
     from .models.kaditar import kaditar_spec
     from .models.sulepel import sulepel_spec
     from .models.zepilix import zepilix_spec
+    from .models.ribozen import ribozen_spec
 
     register_architecture("LlamaForCausalLM", llama_spec)
     register_architecture("llama", llama_spec)
     register_architecture("Sulepel", sulepel_spec)
     register_architecture("Kaditar", kaditar_spec)
     register_architecture("Zepilix", zepilix_spec)
+    register_architecture("Ribozen", ribozen_spec)
 
 
 _register_builtin()
