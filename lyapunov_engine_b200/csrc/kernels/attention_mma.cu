@@ -320,7 +320,8 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
       }
     }
     // a warp skips tiles none of its rows can see (all keys after its last row, or all before its window)
-    const bool visible = k0 <= warp_p_last && (k0 + BN - 1 >= warp_lo_first || it < keep_tiles);
+    // (a tile that holds kept first keys is seen by every warp behind it, wherever it stands among the tiles)
+    const bool visible = k0 <= warp_p_last && (k0 + BN - 1 >= warp_lo_first || k0 < keep_first);
     if (visible) {
       const bf16 *k_tile = k_tiles + stage * BN * HD, *v_tile = v_tiles + stage * BN * HD;
       float s[BN / 8][4];
