@@ -111,9 +111,10 @@ mlstm_scan_kernel(MlstmArgs p) {
       __syncwarp();
       for (int t = threadIdx.x; t < tile; t += gate_threads) {
         const float m_old = s_gate[2 * ML_TILE + t], m_new = s_gate[4 * ML_TILE + t];
-        s_gate[2 * ML_TILE + t] = expf(s_gate[1 * ML_TILE + t] + m_old - m_new);
-        s_gate[3 * ML_TILE + t] = expf(s_gate[0 * ML_TILE + t] - m_new);
-        s_gate[4 * ML_TILE + t] = expf(-m_new);
+        // (factors that multiply up over the sequence: the exponential that does not lean to one side)
+        s_gate[2 * ML_TILE + t] = le::exp_unbiased(s_gate[1 * ML_TILE + t] + m_old - m_new);
+        s_gate[3 * ML_TILE + t] = le::exp_unbiased(s_gate[0 * ML_TILE + t] - m_new);
+        s_gate[4 * ML_TILE + t] = le::exp_unbiased(-m_new);
       }
     }
     for (int i = threadIdx.x; i < tile * D; i += threads) {

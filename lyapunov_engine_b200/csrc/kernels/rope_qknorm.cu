@@ -12,9 +12,12 @@
 //       (u, v) -> ((u cos - v sin) * m, (v cos + u sin) * m)      m: one factor on cosines and sines
 //   q is rewritten in place, k and v go to the pages of the token's position.
 //
-// The angle is position times rate in 32 bits, its cosine and sine are made
-// here (sincosf), so there is no table and no longest position.  Sums, norms
-// and the rotation are 32-bit; every output is rounded once.  `q_count` and
+// The rates come as 64-bit numbers and the angle, position times rate, is
+// taken in 64 bits before its cosine and sine are made here and kept as
+// float32: at position p a 32-bit product would be off by up to p * 2^-24
+// radians, which at a thousand tokens is more than all other rounding of a
+// 32-bit run together.  So there is no table and no longest position.  Sums,
+// norms and the rotation are 32-bit; every output is rounded once.  `q_count` and
 // `k_count` are the real entries the means run over (padding columns are zero
 // and do not count).  One block per token.
 #include "common.cuh"
@@ -27,7 +30,7 @@ template <typename T>
 __global__ void __launch_bounds__(QKN_THREADS)
 rope_qknorm_store_kernel(T *__restrict__ rows, int64_t row_stride, const float *__restrict__ bias,
                          const float *__restrict__ w_q, const float *__restrict__ w_k, float eps, int q_count, int k_count,
-                         const float *__restrict__ rates, int rot, float magnitude, T *__restrict__ k_cache,
+                         const double *__restrict__ rates, int rot, float magnitude, T *__restrict__ k_cache,
                          T *__restrict__ v_cache, const int32_t *__restrict__ positions,
                          const int32_t *__restrict__ request_of_token, const int32_t *__restrict__ block_table,
                          int max_blocks, int heads, int kv_heads, int head_dim, int page_size, int num_pages, int write_kv,
@@ -43,10 +46,10 @@ rope_qknorm_store_kernel(T *__restrict__ rows, int64_t row_stride, const float *
   const int pos = positions[t];
   const int b = request_of_token[t];
   for (int i = threadIdx.x; i < rot / 2; i += QKN_THREADS) {
-    float s, c;
-    sincosf(static_cast<float>(pos) * rates[i], &s, &c);
-    s_cos[i] = c * magnitude;
-    s_sin[i] = s * magnitude;
+    double s, c;
+    sincos(static_cast<double>(pos) * rates[i], &s, &c);
+    s_cos[i] = static_cast<float>(c) * magnitude;
+    s_sin[i] = static_cast<float>(s) * magnitude;
   }
   int page = -1;
   if (write_kv) {
@@ -103,9 +106,9 @@ rope_qknorm_store_kernel(T *__restrict__ rows, int64_t row_stride, const float *
 
 // rows: [T, >= (heads + 2 kv_heads) * head_dim] of type `dtype`, row stride row_stride; bias: float32 [(heads + 2
 // kv_heads) * head_dim] or null; w_q [heads * head_dim], w_k [kv_heads * head_dim] float32 or both null (no norm);
-// rates: float32 [rot / 2]; caches [num_pages, kv_heads, page_size, head_dim].  write_kv 0: queries only.
+// rates: float64 [rot / 2]; caches [num_pages, kv_heads, page_size, head_dim].  write_kv 0: queries only.
 LE_API int le_rope_qknorm_store(void *rows, int64_t row_stride, int dtype, const float *bias, const float *w_q,
-                                const float *w_k, float eps, int q_count, int k_count, const float *rates, int rot,
+                                const float *w_k, float eps, int q_count, int k_count, const double *rates, int rot,
                                 float magnitude, void *k_cache, void *v_cache, const int32_t *positions,
                                 const int32_t *request_of_token, const int32_t *block_table, int max_blocks, int num_tokens,
                                 int heads, int kv_heads, int head_dim, int page_size, int num_pages, int write_kv, int *status,

@@ -11,8 +11,8 @@
 // B and C are shared by the rows of a group (`rows_per_group` consecutive
 // rows).  Both forms of the design family run here: one decay per head and
 // step sizes per head (state-space duality), or decays per row and state and
-// step sizes per row (the selective scan).  Step sizes, decays, the
-// recurrence, the sum and the gate are 32-bit; x, B, C, dt_raw and z come in
+// step sizes per row (the selective scan).  Step sizes, decays (le::exp_unbiased:
+// they multiply up over the whole sequence), the recurrence, the sum and the gate are 32-bit; x, B, C, dt_raw and z come in
 // the activations' type; the state is float32 [state rows, rows, N].
 //
 // A block takes one request and ROWS consecutive rows of one group; a row has
@@ -127,12 +127,12 @@ ssm_scan_kernel(SsmArgs p) {
         const float dx = dv * xv;
         float acc = 0.0f;
         float decay_all = 0.0f;
-        if constexpr (!PER_ROW) decay_all = expf(dv * a[0]);
+        if constexpr (!PER_ROW) decay_all = le::exp_unbiased(dv * a[0]);
 #pragma unroll
         for (int j = 0; j < NPER; ++j) {
           const int n = lane + LANES * j;
           if (n < N) {
-            const float decay = PER_ROW ? expf(dv * a[j]) : decay_all;
+            const float decay = PER_ROW ? le::exp_unbiased(dv * a[j]) : decay_all;
             S[j] = fmaf(decay, S[j], dx * s_b[t * N + n]);
             acc = fmaf(S[j], s_c[t * N + n], acc);
           }

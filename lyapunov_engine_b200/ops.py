@@ -1514,7 +1514,8 @@ def rope_qknorm_store(rows, bias, w_q, w_k, eps, q_count, k_count, rates, rot, m
     whole (and k as a whole) is divided by sqrt(sum of squares / ``q_count`` +
     eps) and multiplied by ``w_q`` (``w_k``), float32, both None for no norm;
     in every head of q and k entry i < rot / 2 turns with entry i + rot / 2 by
-    position * rates[i], cosine and sine times ``magnitude``.  Queries are
+    position * rates[i] (``rates`` float64: the angle is taken in 64 bits),
+    cosine and sine times ``magnitude``.  Queries are
     rewritten in place; keys and values go to the caches' pages when
     ``write_kv``."""
     _need_cuda(rows, bias, w_q, w_k, rates, k_cache, v_cache, positions, block_table)
@@ -1525,7 +1526,7 @@ def rope_qknorm_store(rows, bias, w_q, w_k, eps, q_count, k_count, rates, rot, m
     assert (w_q is None) == (w_k is None)
     assert w_q is None or (w_q.dtype == torch.float32 and w_q.numel() == heads * head_dim and w_k.dtype == torch.float32
                            and w_k.numel() == kv_heads * head_dim and w_q.is_contiguous() and w_k.is_contiguous())
-    assert rates.dtype == torch.float32 and rates.is_contiguous() and rates.numel() >= rot // 2
+    assert rates.dtype == torch.float64 and rates.is_contiguous() and rates.numel() >= rot // 2
     pages = 0
     if write_kv:
         assert k_cache.dtype == rows.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()

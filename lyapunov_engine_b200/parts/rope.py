@@ -155,12 +155,11 @@ def ramped_rates(rot: int, base: float, scaling: dict | None) -> tuple[torch.Ten
     (2 ln base); between lo = max(floor(d(fast)), 0) and hi = min(ceil(d(slow)),
     rot - 1) a ramp r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) blends
     f_i (fast pairs, r = 0) into f_i / factor (slow pairs, r = 1), and cosines
-    and sines are multiplied by 0.1 ln(factor) + 1.  Made in 64 bits, kept as
-    float32."""
+    and sines are multiplied by 0.1 ln(factor) + 1.  64-bit numbers."""
     i = torch.arange(max(rot, 2) // 2, dtype=torch.float64)
     rates = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / max(rot, 2))
     if not scaling:
-        return rates.to(torch.float32), 1.0
+        return rates, 1.0
     factor, original = float(scaling["factor"]), float(scaling["original"])
 
     def pair_of(turns: float) -> float:
@@ -170,7 +169,7 @@ def ramped_rates(rot: int, base: float, scaling: dict | None) -> tuple[torch.Ten
     hi = min(math.ceil(pair_of(float(scaling["slow"]))), rot - 1)
     ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
     rates = rates / factor * ramp + rates * (1.0 - ramp)
-    return rates.to(torch.float32), 0.1 * math.log(factor) + 1.0
+    return rates, 0.1 * math.log(factor) + 1.0
 
 
 @register_position_encoding("rotary_normed")
@@ -181,8 +180,9 @@ class NormedRotaryEncoding(PositionEncoding):
     (``bias_names``), and a norm over the whole of q and over the whole of k
     (not per head): x / sqrt(mean(x^2) + eps) * w with ``q_norm_name`` [heads
     * head_dim] and ``k_norm_name`` [kv_heads * head_dim].  ``scaling``: see
-    ramped_rates.  No table: angle, cosine and sine are made in 32 bits from
-    the step's own positions.  ``head_dim`` is the real size of queries and
+    ramped_rates.  No table: the angle (position times a 64-bit rate, taken
+    in 64 bits) and its cosine and sine (kept in 32 bits) are made from the
+    step's own positions.  ``head_dim`` is the real size of queries and
     keys (``value_dim`` of values); the heads the kernels see may be padded
     with zeros behind it (``set_geometry``)."""
     padded_heads_ok = True
