@@ -212,9 +212,15 @@ def expert(h, w, p, round_to):
     return _r(a @ w[p + "down"].T, round_to)
 
 
-def routed_experts(h, w, p, mlp, round_to):
+def routed_experts(h, w, p, mlp, round_to, margins=None):
+    """``margins``: a list that receives, per token, how far the last chosen
+    router logit lies above the first one not chosen (inf where all are chosen)."""
     experts, top = mlp["router"]["experts"], mlp["router"]["top"]
-    scores = torch.sigmoid(h @ w[p + "router"].T)
+    logits = h @ w[p + "router"].T
+    if margins is not None:
+        ordered = torch.sort(logits, dim=-1, descending=True).values
+        margins.append(ordered[:, top - 1] - ordered[:, top] if experts > top else torch.full_like(ordered[:, 0], math.inf))
+    scores = torch.sigmoid(logits)
     out = torch.zeros_like(h)
     chosen = torch.topk(scores, top, dim=-1).indices
     for t in range(h.shape[0]):
@@ -226,9 +232,10 @@ def routed_experts(h, w, p, mlp, round_to):
 
 
 # ------------------------------------------------------------------ the model
-def forward(config, weights, tokens, dtype=torch.float64, round_to=None, layers_out=None):
+def forward(config, weights, tokens, dtype=torch.float64, round_to=None, layers_out=None, margins_out=None):
     """Logits [T, vocab] of one whole sequence.  ``layers_out``: a list that
-    receives the stream after every layer."""
+    receives the stream after every layer.  ``margins_out``: a list that
+    receives every routed layer's margins (see routed_experts)."""
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in weights.items()}
     eps = config["norm"]["eps"]
     x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)] * config["embedding"]["scale"]
@@ -251,7 +258,103 @@ def forward(config, weights, tokens, dtype=torch.float64, round_to=None, layers_
         x = x + y * w[p + "ls1"]
         if layer.get("mlp") is not None:
             h = norm(x, p + "norm2")
-            x = x + routed_experts(h, w, p + "mlp.", layer["mlp"], round_to) * w[p + "ls2"]
+            x = x + routed_experts(h, w, p + "mlp.", layer["mlp"], round_to, margins_out) * w[p + "ls2"]
         if layers_out is not None:
             layers_out.append(x.clone())
     return norm(x, "final.norm") @ w["head"].T
+
+
+def greedy(config, weights, prompt, n):
+    ids = list(prompt)
+    out = []
+    for _ in range(n):
+        nxt = int(forward(config, weights, ids)[-1].argmax())
+        out.append(nxt)
+        ids.append(nxt)
+    return out
+
+
+# ------------------------------------------------------------------ tensors
+def tensor_shapes(config):
+    W, V = config["width"], config["vocab"]
+    shapes = {"embed": (V, W), "final.norm": (W,), "head": (V, W)}
+    for i, layer in enumerate(config["layers"]):
+        p, m = f"l{i}.", layer["mixer"]
+        shapes[p + "norm1"] = shapes[p + "ls1"] = (W,)
+        q = p + "mix."
+        if layer["type"] == "mlstm":
+            H, d, e = m["heads"], m["dim"], m["vdim"]
+            shapes.update({q + "q": (H * d, W), q + "k": (H * d, W), q + "v": (H * e, W), q + "g": (H * e, W),
+                           q + "o": (W, H * e), q + "norm": (H * e,), q + "i": (H, W), q + "i.b": (H,), q + "f": (H, W),
+                           q + "f.b": (H,)})
+        elif layer["type"] == "mamba2":
+            H, e, N, G = m["heads"], m["vdim"], m["state"], m["groups"]
+            inner, C = H * e, H * e + 2 * G * N
+            shapes.update({q + "in": (2 * inner + 2 * G * N + H, W), q + "conv": (C, m["conv"]), q + "conv.b": (C,),
+                           q + "dt_bias": (H,), q + "A_log": (H,), q + "D": (H,), q + "norm": (inner,), q + "o": (W, inner)})
+        else:
+            a, s = m["left"], m["right"]
+            H, G, d, e = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+            l, r = q + "left.", q + "right."
+            shapes.update({l + "q": (H * d, W), l + "q.b": (H * d,), l + "k": (G * d, W), l + "k.b": (G * d,),
+                           l + "v": (G * e, W), l + "v.b": (G * e,), l + "q.norm": (H * d,), l + "k.norm": (G * d,),
+                           l + "g": (H * e, W), l + "o": (W, H * e)})
+            C, N, R = s["inner"], s["state"], s["dt_rank"]
+            shapes.update({r + "in": (2 * C, W), r + "conv": (C, s["conv"]), r + "conv.b": (C,), r + "x": (R + 2 * N, C),
+                           r + "dt": (C, R), r + "dt.b": (C,), r + "A_log": (C, N), r + "D": (C,), r + "o": (W, C)})
+        mlp = layer.get("mlp")
+        if mlp is not None:
+            shapes[p + "norm2"] = shapes[p + "ls2"] = (W,)
+            F = mlp["expert"]["ff"]
+            for e in range(mlp["router"]["experts"]):
+                shapes.update({f"{p}mlp.e{e}.gate": (F, W), f"{p}mlp.e{e}.up": (F, W), f"{p}mlp.e{e}.down": (W, F)})
+            shapes[p + "mlp.router"] = (mlp["router"]["experts"], W)
+            if mlp.get("shared") is not None:
+                S = mlp["shared"]["ff"]
+                shapes.update({p + "mlp.shared.gate": (S, W), p + "mlp.shared.up": (S, W), p + "mlp.shared.down": (W, S)})
+    return shapes
+
+
+def random_weights(config, seed, sharp=3.0):
+    """Values of bfloat16 precision (so that a folder stored in either type
+    holds the same model).  Matrices N(0, 1 / fan-in) times a factor; norm
+    weights of queries and keys are large enough that single keys decide a
+    softmax (``sharp``: roughly the spread of the scores before the config's
+    scale); step sizes and decays are spread so that some channels remember
+    hundreds of tokens and others a few; routers are wide apart."""
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, shape in tensor_shapes(config).items():
+        tail = name.split(".", 1)[1] if name.startswith("l") and "." in name else name
+        n = lambda *s: torch.randn(s or shape, generator=g)
+        u = lambda lo, hi: lo + (hi - lo) * torch.rand(shape, generator=g)
+        if tail in ("norm1", "norm2", "mix.norm") or name == "final.norm":
+            t = 1.0 + 0.2 * n()
+        elif tail in ("ls1", "ls2"):
+            t = u(0.4, 1.3)
+        elif tail in ("mix.left.q.norm", "mix.left.k.norm"):
+            t = math.sqrt(sharp) * (1.0 + 0.3 * n())
+        elif tail.endswith("conv"):
+            t = 0.6 * n()
+        elif tail == "mix.A_log":
+            t = u(-4.0, 0.5)
+        elif tail == "mix.right.A_log":
+            t = u(-3.0, 1.0)
+        elif tail in ("mix.dt_bias", "mix.right.dt.b"):
+            t = u(-4.0, 0.0)
+        elif tail in ("mix.D", "mix.right.D"):
+            t = 1.0 + 0.3 * n()
+        elif tail == "mix.f.b":
+            t = u(1.0, 5.0)
+        elif len(shape) == 1:
+            t = 0.3 * n()
+        elif name == "embed":
+            t = n()
+        else:
+            t = n() / math.sqrt(shape[1])
+            if tail == "mlp.router":
+                t = t * 4.0
+            if tail.endswith(".o") or tail.endswith(".down"):
+                t = t * 0.5
+        out[name] = t.to(torch.bfloat16).to(torch.float64)
+    return out
