@@ -1606,6 +1606,325 @@ def run_zepilix(args):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------- Ribozen
+RIBOZEN_WINDOW = 1024       # keys an attention layer's query sees at most, beside the first RIBOZEN_KEPT
+RIBOZEN_KEPT = 4
+RIBOZEN_STATE = 128         # numbers of state per channel of a state-space-duality layer
+RIBOZEN_SCAN_STATE = 16     # of a selective-scan channel
+RIBOZEN_EXPERTS, RIBOZEN_TOP = 8, 2
+
+
+def ribozen_config(llama: dict) -> dict:
+    """A Ribozen model with the width, heads, head size, vocabulary and number of layers of the given Llama shapes:
+    state-space duality, state-space duality, matrix memory, attention beside a selective scan, and so on; every
+    layer has eight routed experts (two per token) and a shared one, each a quarter of the Llama feed-forward's
+    size, so that a token's feed-forward products are three quarters of the Llama layer's."""
+    nh, nkv, hd, W = llama["num_attention_heads"], llama["num_key_value_heads"], llama["head_dim"], llama["hidden_size"]
+    ff = llama["intermediate_size"] // 4
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": RIBOZEN_EXPERTS, "top": RIBOZEN_TOP}, "shared": {"ff": ff}}
+    duality = {"type": "mamba2", "mlp": mlp,
+               "mixer": {"heads": 2 * W // 64, "vdim": 64, "state": RIBOZEN_STATE, "groups": 8, "conv": 4, "norm_groups": 8}}
+    memory = {"type": "mlstm", "mlp": mlp, "mixer": {"heads": W // 256, "dim": 128, "vdim": 256, "gate_cap": 15.0}}
+    pair = {"type": "parallel", "mlp": mlp,
+            "mixer": {"left_scale": 0.6, "right_scale": 1.1,
+                      "left": {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "softcap": 50.0,
+                               "rot": {"dims": hd, "base": 500000.0,
+                                       "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}},
+                               "mask": {"size": RIBOZEN_WINDOW, "keep_first": RIBOZEN_KEPT}},
+                      "right": {"inner": W, "state": RIBOZEN_SCAN_STATE, "dt_rank": W // 16, "conv": 4}}}
+    kinds = (duality, duality, memory, pair)
+    return {"architecture": "Ribozen", "vocab": llama["vocab_size"], "width": W, "norm": {"eps": 1e-5},
+            "embedding": {"scale": W ** 0.5}, "layers": [kinds[i % 4] for i in range(llama["num_hidden_layers"])]}
+
+
+def ribozen_decode_bytes(cfg, batch, context):
+    """Bytes one decode step of a Ribozen model must move: the bfloat16 weights it touches (of the routed experts
+    those that batch * top tokens can reach), each live request's states read and written (32-bit), and its window
+    of keys and values."""
+    W, V = cfg["width"], cfg["vocab"]
+    total = 2 * 2 * V * W + 4 * W
+    for layer in cfg["layers"]:
+        m, f = layer["mixer"], layer["mlp"]
+        F, E, top, S = f["expert"]["ff"], f["router"]["experts"], f["router"]["top"], f["shared"]["ff"]
+        total += 2 * 3 * W * (F * min(E, batch * top) + S) + 4 * E * W + 4 * 4 * W
+        if layer["type"] == "mamba2":
+            H, P, N, G = m["heads"], m["vdim"], m["state"], m["groups"]
+            inner, C = H * P, H * P + 2 * G * N
+            total += 2 * ((2 * inner + 2 * G * N + H) * W + W * inner) + batch * (2 * 4 * inner * N + 2 * 4 * (m["conv"] - 1) * C)
+        elif layer["type"] == "mlstm":
+            H, d, e = m["heads"], m["dim"], m["vdim"]
+            total += 2 * ((2 * H * d + 2 * H * e + 2 * H) * W + W * H * e) + batch * 2 * 4 * H * (e + 1) * d
+        else:
+            a, r = m["left"], m["right"]
+            nh, G, d, e = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+            seen = min(context, a["mask"]["size"] + a["mask"]["keep_first"])
+            total += 2 * ((nh * d + G * d + G * e + nh * e) * W + W * nh * e) + 2 * batch * seen * G * (d + e)
+            C, N, R = r["inner"], r["state"], r["dt_rank"]
+            total += 2 * (2 * C * W + (R + 2 * N) * C + C * R + W * C) + 4 * C * N + batch * (2 * 4 * C * N + 2 * 4 * (r["conv"] - 1) * C)
+    return total
+
+
+def ribozen_prefill_flops(cfg, tokens):
+    """(flops of the matrix products and the attentions as computed here, flops of the recurrences, which run on the
+    FP32 pipes: six per entry of a state-space state and token, four per entry of a matrix memory)."""
+    W, V = cfg["width"], cfg["vocab"]
+    flops, scan = 2 * V * W, 0
+    for layer in cfg["layers"]:
+        m, f = layer["mixer"], layer["mlp"]
+        F, E, top, S = f["expert"]["ff"], f["router"]["experts"], f["router"]["top"], f["shared"]["ff"]
+        flops += 2 * tokens * (3 * W * (top * F + S) + E * W)
+        if layer["type"] == "mamba2":
+            H, P, N, G = m["heads"], m["vdim"], m["state"], m["groups"]
+            flops += 2 * tokens * ((2 * H * P + 2 * G * N + H) * W + W * H * P)
+            scan += 6 * tokens * H * P * N
+        elif layer["type"] == "mlstm":
+            H, d, e = m["heads"], m["dim"], m["vdim"]
+            flops += 2 * tokens * ((2 * H * d + 2 * H * e + 2 * H) * W + W * H * e)
+            scan += 4 * tokens * H * d * (e + 1)
+        else:
+            a, r = m["left"], m["right"]
+            nh, G, d, e = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+            w = a["mask"]["size"]
+            seen = tokens * (tokens + 1) // 2 if tokens <= w else w * (w + 1) // 2 + (tokens - w) * (w + a["mask"]["keep_first"])
+            flops += 2 * tokens * ((nh * d + G * d + G * e + nh * e) * W + W * nh * e) + 2 * nh * (d + e) * seen
+            C, N, R = r["inner"], r["state"], r["dt_rank"]
+            flops += 2 * tokens * (2 * C * W + (R + 2 * N) * C + C * R + W * C)
+            scan += 6 * tokens * C * N
+    return flops, scan
+
+
+def ribozen_kernel_rows(pk, llama):
+    """Each kernel the design adds, alone, beside the like kernel of the closest existing path at like sizes:
+    microseconds per launch inside a captured graph over rotating tensors, the share of the measured copy bandwidth
+    that the bytes it must move make, and for the recurrences their share of the FP32 pipes."""
+    import torch
+
+    from lyapunov_engine_b200 import ops
+    from lyapunov_engine_b200.parts.rope import pair_rates, ramped_rates
+
+    dev = "cuda:0"
+    cfg = ribozen_config(llama)
+    W, nh, nkv, hd = llama["hidden_size"], llama["num_attention_heads"], llama["num_key_value_heads"], llama["head_dim"]
+    page = BLOCK_SIZE
+    rows = []
+
+    def row(kernel, like, tokens, nbytes, launch, sets, fp32_flops=0):
+        us = graph_median_us(launch, sets)
+        entry = {"kernel": kernel, "like": like, "tokens": tokens, "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1),
+                 "hbm_frac": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)}
+        if fp32_flops:
+            # 148 multiprocessors x 128 lanes x 2 flops at the highest clock (1,965 MHz): 74.4 TFLOP/s
+            entry["fp32_frac"] = round(fp32_flops / us / 1e6 / 74.4, 3)
+        rows.append(entry)
+
+    bf = torch.bfloat16
+    status = ops.new_status(dev)
+    dm, mm, pm = cfg["layers"][0]["mixer"], cfg["layers"][2]["mixer"], cfg["layers"][3]["mixer"]
+    for T in (8, 2048):
+        reqs = T if T <= 64 else 1
+        q_lens = [T // reqs] * reqs
+        cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=dev)
+        slots = torch.arange(reqs, dtype=torch.int32, device=dev)
+        state_sets = 4 if T <= 64 else 2
+        # state-space duality: one decay per head
+        H, P, N, G = dm["heads"], dm["vdim"], dm["state"], dm["groups"]
+        inner, C = H * P, H * P + 2 * G * N
+        conv = torch.randn(T, C, device=dev).to(bf)
+        proj = torch.randn(T, inner + H + 8, device=dev).to(bf)
+        y = torch.empty(T, inner, device=dev)
+        states = [torch.zeros(reqs + 1, inner, N, device=dev) for _ in range(state_sets)]
+        zeros_h = torch.zeros(H, device=dev)
+        row(f"state-space recurrence, {H} heads of {P} x {N} (one decay per head), {reqs} request(s)",
+            "delta rule, 16 heads of 128 x 128", T, reqs * 2 * 4 * inner * N + T * (C * 2 + inner * 6 + H * 2),
+            lambda i: ops.ssm_scan(y, conv[:, :inner], conv, inner, inner + G * N, proj[:, inner:inner + H], proj[:, :inner], zeros_h,
+                                   zeros_h, zeros_h, states[i], slots, cu, reqs, N, P, (H // G) * P, per_row=False), state_sets,
+            fp32_flops=6 * T * inner * N)
+        normed = torch.empty(T, inner, device=dev, dtype=bf)
+        wn = torch.ones(inner, device=dev)
+        row("norm in 8 parts of the gated channels", "norm per head times silu gate", T, T * inner * 6,
+            lambda i: ops.rmsnorm(normed, y, None, wn, 1e-5, groups=8), 1)
+        del states
+        # selective scan: a decay per channel and state
+        r = pm["right"]
+        Cs, Ns, R = r["inner"], r["state"], r["dt_rank"]
+        convs = torch.randn(T, Cs, device=dev).to(bf)
+        low = torch.randn(T, (R + 2 * Ns + 7) // 8 * 8, device=dev).to(bf)
+        dt = torch.randn(T, Cs, device=dev).to(bf)
+        z = torch.randn(T, Cs, device=dev).to(bf)
+        outs = torch.empty(T, Cs, device=dev, dtype=bf)
+        states = [torch.zeros(reqs + 1, Cs, Ns, device=dev) for _ in range(state_sets)]
+        a_log, zeros_c = torch.zeros(Cs, Ns, device=dev), torch.zeros(Cs, device=dev)
+        row(f"state-space recurrence, {Cs} channels x {Ns} (a decay per channel and state), {reqs} request(s)",
+            "delta rule, 16 heads of 128 x 128", T, reqs * 2 * 4 * Cs * Ns + 4 * Cs * Ns + T * (Cs * 8 + Ns * 4),
+            lambda i: ops.ssm_scan(outs, convs, low, R, R + Ns, dt, z, zeros_c, a_log, zeros_c, states[i], slots, cu, reqs, Ns, 1, Cs,
+                                   per_row=True, out_scale=1.1), state_sets, fp32_flops=6 * T * Cs * Ns)
+        del states
+        # matrix memory
+        Hm, d, e = mm["heads"], mm["dim"], mm["vdim"]
+        width = (2 * Hm * d + 2 * Hm * e + 2 * Hm + 7) // 8 * 8
+        rows_m = torch.randn(T, width, device=dev).to(bf)
+        o = torch.empty(T, Hm * e, device=dev)
+        states = [torch.zeros(reqs + 1, *ops.mlstm_state_shape(Hm, d, e), device=dev) for _ in range(state_sets)]
+        zeros_m = torch.zeros(Hm, device=dev)
+        row(f"matrix memory, {Hm} heads of {d} x {e}, {reqs} request(s)", "delta rule, 16 heads of 128 x 128", T,
+            reqs * 2 * states[0][0].numel() * 4 + T * (width * 2 + Hm * e * 4),
+            lambda i: ops.mlstm_scan(o, rows_m, 0, Hm * d, 2 * Hm * d, 2 * Hm * d + 2 * Hm * e, 2 * Hm * d + 2 * Hm * e + Hm, zeros_m,
+                                     zeros_m, states[i], slots, cu, reqs, Hm, d, e, 15.0, d ** -0.5), state_sets,
+            fp32_flops=4 * T * Hm * d * (e + 1))
+        gated = torch.empty(T, Hm * e, device=dev, dtype=bf)
+        wm = torch.ones(Hm * e, device=dev)
+        row("norm per head (a weight per head) times sigmoid gate", "norm per head times silu gate", T, T * Hm * e * 8,
+            lambda i: ops.head_norm_gate(gated, o, rows_m[:, 2 * Hm * d + Hm * e:2 * Hm * d + 2 * Hm * e], wm, 1e-5, Hm, e, sigmoid=True), 1)
+        del states
+        # the delta rule at its own sizes, as the yardstick of the recurrences
+        Hd, Gd, dd = W // 128, W // 256, 128
+        Cd = 2 * Gd * dd + Hd * dd
+        wd = (Cd + Hd * dd + 2 * Hd + 7) // 8 * 8
+        projd = torch.randn(T, wd, device=dev).to(bf)
+        convd = torch.randn(T, Cd, device=dev).to(bf)
+        od = torch.empty(T, Hd * dd, device=dev)
+        states = [torch.zeros(reqs + 1, Hd, dd, dd, device=dev) for _ in range(state_sets)]
+        zeros_d = torch.zeros(Hd, device=dev)
+        row(f"delta rule, {Hd} heads of {dd} x {dd}, {reqs} request(s)", "", T, reqs * 2 * 4 * Hd * dd * dd + T * (Cd * 2 + Hd * dd * 4),
+            lambda i: ops.gated_delta_scan(od, convd, 0, Gd * dd, 2 * Gd * dd, projd, Cd + Hd * dd, Cd + Hd * dd + Hd, zeros_d, zeros_d,
+                                           states[i], slots, cu, reqs, Hd, Gd, dd, dd, 1e-6, dd ** -0.5), state_sets,
+            fp32_flops=6 * T * Hd * dd * dd)
+        del states
+        # bias, norm over whole projections, turn, cache write; beside the turn of pairs with its norm per head
+        pages = (T + page - 1) // page + 1
+        btab = torch.arange(pages, dtype=torch.int32, device=dev).view(1, -1).contiguous()
+        req0 = torch.zeros(T, dtype=torch.int32, device=dev)
+        pos = torch.arange(T, dtype=torch.int32, device=dev)
+        qkv = torch.randn(T, (2 * nh + 2 * nkv) * hd, device=dev).to(bf)
+        kc = torch.zeros(pages + 1, nkv, page, hd, device=dev, dtype=bf)
+        vc = torch.zeros_like(kc)
+        rates, magnitude = ramped_rates(hd, 5e5, {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0})
+        rates = rates.to(dev)
+        bias = torch.zeros((nh + 2 * nkv) * hd, device=dev)
+        wq, wk = torch.ones(nh * hd, device=dev), torch.ones(nkv * hd, device=dev)
+        row("bias + norm over all of q and of k + turn of halves + cache write", "turn of pairs + norm + cache write", T,
+            T * ((nh + nkv) * hd * 4 + nkv * hd * 4) + 4 * (2 * nh + 3 * nkv) * hd,
+            lambda i: ops.rope_qknorm_store(qkv, bias, wq, wk, 1e-5, nh * hd, nkv * hd, rates, hd, magnitude, kc, vc, pos, req0, btab,
+                                            nh, nkv, hd, page, True, status), 1)
+        qk = torch.randn(T, (nh + nkv) * hd, device=dev).to(bf)
+        rates_p = pair_rates(hd, 5e5).to(dev)
+        row("turn of pairs + norm + cache write (values are the keys)", "", T, T * ((nh + nkv) * hd * 4 + nkv * hd * 2),
+            lambda i: ops.rope_norm_store(qk, kc, vc, rates_p, pos, req0, btab, nh, nkv, hd, 0, hd, 1e-6, hd, page, True, True, status), 1)
+        attn = torch.randn(T, nh * hd, device=dev).to(bf)
+        side = torch.empty(T, nh * hd + W, device=dev, dtype=bf)
+        row("gate per entry (sigmoid) into the shared buffer", "norm per head times silu gate", T, T * nh * hd * 6,
+            lambda i: ops.sigmoid_gate(side[:, :nh * hd], attn, qkv[:, (nh + 2 * nkv) * hd:], 0.6), 1)
+        # the layer scale in the norm's kernel
+        resid = [torch.randn(T, W, device=dev) for _ in range(8)]
+        delta = torch.randn(T, W, device=dev).to(bf)
+        normed_w = torch.empty(T, W, device=dev, dtype=bf)
+        w1, ls = torch.ones(W, device=dev), torch.ones(W, device=dev)
+        row("rmsnorm + residual with a factor per column", "rmsnorm + residual", T, T * W * 12 + 8 * W,
+            lambda i: ops.rmsnorm(normed_w, resid[i], delta, w1, 1e-5, delta_scale=ls), 8)
+        row("rmsnorm + residual", "", T, T * W * 12 + 4 * W, lambda i: ops.rmsnorm(normed_w, resid[i], delta, w1, 1e-5), 8)
+        del resid
+    # attention over a window with kept first keys and capped scores, beside the same window plain
+    for label, q_lens, ctx in (("decode, 8 requests at 4,096", [1] * 8, [4095] * 8), ("prompt of 2,048", [2048], [0])):
+        T = sum(q_lens)
+        B = len(q_lens)
+        total = [c + n for c, n in zip(ctx, q_lens)]
+        per = (max(total) + page - 1) // page
+        btab = torch.arange(B * per, dtype=torch.int32, device=dev).view(B, per).contiguous()
+        kc = torch.randn(B * per + 1, nkv, page, hd, device=dev).to(bf)
+        vc = torch.randn(B * per + 1, nkv, page, hd, device=dev).to(bf)
+        q = torch.randn(T, nh * hd, device=dev).to(bf)
+        out = torch.empty(T, nh * hd, device=dev, dtype=bf)
+        cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=dev)
+        before = torch.tensor(ctx, dtype=torch.int32, device=dev)
+        seen = sum(min(t, RIBOZEN_WINDOW + RIBOZEN_KEPT) for t in total) if T == B else \
+            sum(min(p + 1, RIBOZEN_WINDOW + RIBOZEN_KEPT) for p in range(2048)) // 128       # keys a 128-row tile reads, roughly
+        nbytes = (seen if T == B else 2048 * 16 // 128 * 0 + 16 * (RIBOZEN_WINDOW + 128)) * nkv * hd * 4 + T * nh * hd * 4
+        for name, keep, cap in (("kept first keys + capped scores", RIBOZEN_KEPT, 50.0), ("window alone", 0, 0.0)):
+            if T == B:
+                splits = 4
+                scratch = torch.zeros(max(ops.attention_decode_scratch_floats(hd, B, nh, splits), 1), device=dev)
+                launch = lambda i, keep=keep, cap=cap: ops.attention_decode_bf16(
+                    out, scratch, q, q.stride(0), kc, vc, btab, cu, before, None, B, nh, nkv, hd, page, RIBOZEN_WINDOW, hd ** -0.5, splits,
+                    status, keep_first=keep, softcap=cap)
+            else:
+                req = torch.zeros(T // 128, dtype=torch.int32, device=dev)
+                q0 = torch.arange(0, T, 128, dtype=torch.int32, device=dev)
+                launch = lambda i, keep=keep, cap=cap: ops.attention_prefill_bf16(
+                    out, q, q.stride(0), kc, vc, btab, cu, before, req, q0, T // 128, nh, nkv, hd, page, RIBOZEN_WINDOW, hd ** -0.5, status,
+                    keep_first=keep, softcap=cap)
+            row(f"attention (mma.sync), window of {RIBOZEN_WINDOW}: {name}; {label}", "" if keep == 0 else "window alone", T, nbytes, launch, 1)
+        if T != B and ops.attention_tc_available(hd, page):
+            launch = lambda i: ops.attention_prefill_tc_bf16(out, q, q.stride(0), kc, vc, btab, cu, before, req, q0, T // 128, nh, nkv, hd,
+                                                              page, RIBOZEN_WINDOW, hd ** -0.5, status)
+            row(f"attention (tcgen05), window of {RIBOZEN_WINDOW}: window alone; {label}", "", T, nbytes, launch, 1)
+    ops.check_status(status)
+    return rows
+
+
+def run_ribozen(args):
+    """--only ribozen: decode (1 and 8 requests at --context) and prefill (2,048 tokens) of a Ribozen model beside the
+    Zepilix model (the closest existing design: a recurrence with a matrix of state per head, short convolutions, a
+    windowed attention, state rows per request) and the Llama model of the same width, heads, layers and vocabulary
+    (random weights, bfloat16), and the design's own kernels alone beside their likes."""
+    global BLOCK_SIZE
+    import torch
+
+    BLOCK_SIZE = args.page
+    pk = peaks()
+    context = args.context or CONTEXT
+    if args.profile_step:
+        llama = dict(SHAPES[args.shapes])
+        llama["num_hidden_layers"] = args.layers or 4
+        rig = make_rig(ribozen_config(llama), context, 8, args.page)
+        rig.runner.use_cuda_graphs = False
+        if args.profile_step == "decode":
+            ms, _, _ = rig.timed_decode(args.batch, 2, 2, context)
+        else:
+            ms = rig.timed_prefill(args.tokens or PREFILL_TOKENS, 1, 2)
+        print(json.dumps({"only": "ribozen", "profile_step": args.profile_step, "layers": llama["num_hidden_layers"], "ms": round(ms, 3)}))
+        return 0
+    out = {"only": "ribozen", "peaks": pk["source"], "context": context, "sizes": {}}
+    for name in ([args.shapes] if args.shapes != "1b" or args.layers else ["1b", "3b"]):
+        llama = dict(SHAPES[name])
+        if args.layers:
+            llama["num_hidden_layers"] = args.layers
+        res = {}
+        for label, cfg in (("ribozen", ribozen_config(llama)), ("zepilix", zepilix_config(llama)), ("llama", llama)):
+            rig = make_rig(cfg, context, 8, args.page)
+            for b in (1, 8):
+                rig.timed_decode(b, 3, 2, context - 200)
+                ms, graph_steps, _ = rig.timed_decode(b, 24, 6, context)
+                nbytes = {"ribozen": ribozen_decode_bytes, "zepilix": zepilix_decode_bytes, "llama": decode_bytes}[label](cfg, b, context - 12)
+                res[f"{label}_decode_b{b}_ms"] = round(ms, 4)
+                res[f"{label}_decode_b{b}_tokens_per_s"] = round(b * 1000.0 / ms, 1)
+                res[f"{label}_decode_b{b}_hbm_frac"] = round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+                res[f"{label}_decode_b{b}_graph_steps"] = graph_steps
+            ms = rig.timed_prefill(PREFILL_TOKENS, 3, 2)
+            if label == "ribozen":
+                flops, scan = ribozen_prefill_flops(cfg, PREFILL_TOKENS)
+                res["ribozen_prefill_fp32_recurrence_gflop"] = round(scan / 1e9, 2)
+            elif label == "zepilix":
+                flops, scan = zepilix_prefill_flops(cfg, PREFILL_TOKENS)
+                res["zepilix_prefill_fp32_recurrence_gflop"] = round(scan / 1e9, 2)
+            else:
+                flops = prefill_flops(cfg, PREFILL_TOKENS)
+            res[f"{label}_prefill_{PREFILL_TOKENS}_ms"] = round(ms, 3)
+            res[f"{label}_prefill_{PREFILL_TOKENS}_tokens_per_s"] = round(PREFILL_TOKENS * 1000.0 / ms, 1)
+            res[f"{label}_prefill_{PREFILL_TOKENS}_bf16_frac"] = round(flops / (ms * 1e-3) / 1e12 / pk["bf16_tflops"], 4)
+            rig.close()
+            del rig
+            torch.cuda.empty_cache()
+        out["sizes"][name] = res
+        for k, v in res.items():
+            print(f"{name}  {k} = {v}", file=sys.stderr)
+    rows = ribozen_kernel_rows(pk, dict(SHAPES["1b"]))
+    for r in rows:
+        print("  ".join(f"{k}={v}" for k, v in r.items() if v != ""), file=sys.stderr)
+    out["kernels"] = rows
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=1)
@@ -1613,13 +1932,14 @@ def main():
     p.add_argument("--warmup", type=int, default=16)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
-    p.add_argument("--only", choices=["decode", "prefill", "mixed", "serving", "kernels", "sulepel", "kaditar", "zepilix"], default=None,
+    p.add_argument("--only", choices=["decode", "prefill", "mixed", "serving", "kernels", "sulepel", "kaditar", "zepilix", "ribozen"], default=None,
                    help="run one kind of step and exit (for profilers and for further sizes); mixed = --batch decoding "
                         "requests beside one --tokens portion of a prompt in every step; serving = the reference's "
                         "serving benchmark (small model, prompts of 128 tokens, 32 generated: TTFT, ITL, tokens/s); "
                         "kernels = its kernel benchmark (RMSNorm and prefill attention over a grid of sizes); "
                         "sulepel = the Sulepel design beside Llama at equal sizes (decode, prefill, its kernels alone); "
-                        "kaditar = the same for the Kaditar design; zepilix = the Zepilix design beside Sulepel and Llama")
+                        "kaditar = the same for the Kaditar design; zepilix = the Zepilix design beside Sulepel and Llama; "
+                        "ribozen = the Ribozen design beside Zepilix and Llama")
     p.add_argument("--batch-sizes", nargs="+", type=int, default=[1, 4, 8, 16], help="with --only serving")
     p.add_argument("--shapes", choices=sorted(SHAPES), default="1b", help="with --only: layer sizes of Llama-3.2-1B, 3.2-3B or 3.1-8B")
     p.add_argument("--batch", type=int, default=8, help="batch of --only decode")
@@ -1633,7 +1953,7 @@ def main():
     p.add_argument("--without", choices=["norms", "qkv", "attention", "o", "gate_up", "down", "head"], default=None,
                    help="with --only decode (batches up to 16): time the step with this kind of kernel left out")
     p.add_argument("--profile-step", choices=["decode", "prefill"], default=None,
-                   help="with --only sulepel, kaditar or zepilix: run a few steps of that kind launch by launch (no captured graph) on a model of "
+                   help="with --only sulepel, kaditar, zepilix or ribozen: run a few steps of that kind launch by launch (no captured graph) on a model of "
                         "--layers layers (4 by default) and exit; for profilers")
     p.add_argument("--points", choices=["all", "1b"], default="all",
                    help="all: also decode, prefill and the mixed step at the 3B and 8B shapes (context 8192) in `points`")
@@ -1653,6 +1973,8 @@ def main():
         return run_kaditar(args)
     if args.only == "zepilix" and args.impl == "ours":
         return run_zepilix(args)
+    if args.only == "ribozen" and args.impl == "ours":
+        return run_ribozen(args)
     if args.impl == "reference":
         return run_reference(args)
     return run_ours(args)

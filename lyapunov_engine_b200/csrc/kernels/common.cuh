@@ -159,6 +159,16 @@ template <typename T> __device__ __forceinline__ T from_f32(float x);
 template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 
+// The 16 bytes at p (16-byte aligned) as floats: 8 bfloat16 or 4 float32 values.
+template <typename T> struct Piece16 { static constexpr int COUNT = 16 / sizeof(T); };
+template <typename T>
+__device__ __forceinline__ void load_piece16(float (&dst)[Piece16<T>::COUNT], const T *p) {
+  const uint4 raw = *reinterpret_cast<const uint4 *>(p);
+  const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+  for (int v = 0; v < Piece16<T>::COUNT; ++v) dst[v] = to_f32(e[v]);
+}
+
 // 2^x in one instruction (ex2.approx, relative error about 2^-22, results
 // below the normal range flush to zero); exp2f() spends several more on them.
 // For softmax numerators in the bfloat16 kernels; the 32-bit path uses expf.

@@ -31,6 +31,8 @@
 namespace {
 
 constexpr int ML_TILE = 16;
+constexpr int ML_GROUP = 1;        // tokens whose instructions overlap; more than 1 did not pay
+constexpr int ML_AHEAD = 8;        // loads a staging thread has in flight
 constexpr int ML_MAX_THREADS = 256;
 
 __device__ __forceinline__ float log_sigmoid_f32(float x) {
@@ -117,11 +119,45 @@ mlstm_scan_kernel(MlstmArgs p) {
         s_gate[4 * ML_TILE + t] = le::exp_unbiased(-m_new);
       }
     }
-    for (int i = threadIdx.x; i < tile * D; i += threads) {
-      const int t = i / D, d = i - t * D;
-      const T *row = rows + static_cast<int64_t>(first + t0 + t) * p.qkv_stride + head * D + d;
-      s_q[t * D + d] = le::to_f32(row[p.q_col]) * p.q_scale;
-      s_k[t * D + d] = le::to_f32(row[p.k_col]);
+    // q and k of the tile's tokens (every block of a head stages the same ones, so this must be cheap): in 16-byte
+    // pieces where the layout allows, else value by value with ML_AHEAD loads in flight per thread
+    constexpr int PIECE = le::Piece16<T>::COUNT;
+    const bool pieces = D % PIECE == 0 && p.q_col % PIECE == 0 && p.k_col % PIECE == 0 && p.qkv_stride % PIECE == 0 &&
+                        (reinterpret_cast<uintptr_t>(rows) & 15) == 0;
+    if (pieces) {
+      const int per_token = D / PIECE;
+      for (int i = threadIdx.x; i < tile * per_token; i += threads) {
+        const int t = i / per_token, d = (i - t * per_token) * PIECE;
+        const T *row = rows + static_cast<int64_t>(first + t0 + t) * p.qkv_stride + head * D + d;
+        float qv[PIECE], kv[PIECE];
+        le::load_piece16<T>(qv, row + p.q_col);
+        le::load_piece16<T>(kv, row + p.k_col);
+#pragma unroll
+        for (int v = 0; v < PIECE; v += 4) {
+          *reinterpret_cast<float4 *>(s_q + t * D + d + v) =
+              make_float4(qv[v] * p.q_scale, qv[v + 1] * p.q_scale, qv[v + 2] * p.q_scale, qv[v + 3] * p.q_scale);
+          *reinterpret_cast<float4 *>(s_k + t * D + d + v) = make_float4(kv[v], kv[v + 1], kv[v + 2], kv[v + 3]);
+        }
+      }
+    } else {
+      for (int base = threadIdx.x; base < tile * D; base += threads * ML_AHEAD) {
+        float qv[ML_AHEAD], kv[ML_AHEAD];
+#pragma unroll
+        for (int u = 0; u < ML_AHEAD; ++u) {
+          const int i = base + u * threads;
+          qv[u] = kv[u] = 0.0f;
+          if (i < tile * D) {
+            const int t = i / D, d = i - t * D;
+            const T *row = rows + static_cast<int64_t>(first + t0 + t) * p.qkv_stride + head * D + d;
+            qv[u] = le::to_f32(row[p.q_col]), kv[u] = le::to_f32(row[p.k_col]);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < ML_AHEAD; ++u) {
+          const int i = base + u * threads;
+          if (i < tile * D) s_q[i] = qv[u] * p.q_scale, s_k[i] = kv[u];
+        }
+      }
     }
     for (int i = threadIdx.x; i < tile * ROWS; i += threads) {
       const int t = i / ROWS, rr = i - t * ROWS;
@@ -129,23 +165,43 @@ mlstm_scan_kernel(MlstmArgs p) {
     }
     __syncthreads();
     if (has_state) {
-      for (int t = 0; t < tile; ++t) {
-        const float keep = s_gate[2 * ML_TILE + t];
-        const float in = s_gate[3 * ML_TILE + t] * (is_n ? 1.0f : s_v[t * ROWS + r]);
-        float acc = 0.0f;
+      // Tokens in groups of ML_GROUP: the state's chain runs through them one after the other, but each token's
+      // products and the reduction of its sum over the lanes depend on nothing of the others, so a group's
+      // instructions overlap.  A tile's rows beyond its tokens keep everything (factor 1) and take nothing (0).
+      for (int t = 0; t < tile; t += ML_GROUP) {
+        float keep[ML_GROUP], in[ML_GROUP], acc[ML_GROUP];
+#pragma unroll
+        for (int u = 0; u < ML_GROUP; ++u) {
+          const bool live = t + u < tile;
+          keep[u] = live ? s_gate[2 * ML_TILE + t + u] : 1.0f;
+          in[u] = live ? s_gate[3 * ML_TILE + t + u] * (is_n ? 1.0f : s_v[(t + u) * ROWS + r]) : 0.0f;
+          acc[u] = 0.0f;
+        }
 #pragma unroll
         for (int j = 0; j < NPER; ++j) {
           const int d = lane + LANES * j;
           if (d < D) {
-            S[j] = fmaf(keep, S[j], in * s_k[t * D + d]);
-            acc = fmaf(S[j], s_q[t * D + d], acc);
+#pragma unroll
+            for (int u = 0; u < ML_GROUP; ++u) {
+              const int tt = min(t + u, tile - 1);
+              S[j] = fmaf(keep[u], S[j], in[u] * s_k[tt * D + d]);
+              acc[u] = fmaf(S[j], s_q[tt * D + d], acc[u]);
+            }
           }
         }
 #pragma unroll
-        for (int o = LANES / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        for (int o = LANES / 2; o > 0; o >>= 1) {
+#pragma unroll
+          for (int u = 0; u < ML_GROUP; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], o);
+        }
         if (lane == 0) {
-          if (is_n) s_gate[5 * ML_TILE + t] = acc;
-          else s_num[t * ROWS + r] = acc;
+#pragma unroll
+          for (int u = 0; u < ML_GROUP; ++u) {
+            if (t + u < tile) {
+              if (is_n) s_gate[5 * ML_TILE + t + u] = acc[u];
+              else s_num[(t + u) * ROWS + r] = acc[u];
+            }
+          }
         }
       }
     }

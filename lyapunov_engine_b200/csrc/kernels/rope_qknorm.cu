@@ -13,8 +13,8 @@
 //   q is rewritten in place, k and v go to the pages of the token's position.
 //
 // The rates come as 64-bit numbers and the angle, position times rate, is
-// taken in 64 bits before its cosine and sine are made here and kept as
-// float32: at position p a 32-bit product would be off by up to p * 2^-24
+// taken in 64 bits (and brought into [-pi, pi] there) before its cosine and sine are made
+// here in 32: at position p a 32-bit product would be off by up to p * 2^-24
 // radians, which at a thousand tokens is more than all other rounding of a
 // 32-bit run together.  So there is no table and no longest position.  Sums,
 // norms and the rotation are 32-bit; every output is rounded once.  `q_count` and
@@ -36,7 +36,7 @@ rope_qknorm_store_kernel(T *__restrict__ rows, int64_t row_stride, const float *
                          int max_blocks, int heads, int kv_heads, int head_dim, int page_size, int num_pages, int write_kv,
                          int *__restrict__ status) {
   extern __shared__ __align__(16) float qkn_smem[];
-  __shared__ float scratch[33];
+  __shared__ float2 scratch2[QKN_THREADS / 32];
   const int q_width = heads * head_dim, k_width = kv_heads * head_dim;
   float *s_x = qkn_smem;                        // q then k, as floats
   float *s_cos = s_x + q_width + k_width;       // [rot / 2]
@@ -46,10 +46,13 @@ rope_qknorm_store_kernel(T *__restrict__ rows, int64_t row_stride, const float *
   const int pos = positions[t];
   const int b = request_of_token[t];
   for (int i = threadIdx.x; i < rot / 2; i += QKN_THREADS) {
-    double s, c;
-    sincos(static_cast<double>(pos) * rates[i], &s, &c);
-    s_cos[i] = static_cast<float>(c) * magnitude;
-    s_sin[i] = static_cast<float>(s) * magnitude;
+    // the angle in 64 bits, brought into [-pi, pi] there; its cosine and sine in 32
+    double a = static_cast<double>(pos) * rates[i];
+    a -= 6.283185307179586 * rint(a * 0.15915494309189535);
+    float s, c;
+    sincosf(static_cast<float>(a), &s, &c);
+    s_cos[i] = c * magnitude;
+    s_sin[i] = s * magnitude;
   }
   int page = -1;
   if (write_kv) {
@@ -62,16 +65,41 @@ rope_qknorm_store_kernel(T *__restrict__ rows, int64_t row_stride, const float *
   le::wait_for_predecessor();
   T *row = rows + static_cast<int64_t>(t) * row_stride;
   float ss_q = 0.0f, ss_k = 0.0f;
-  for (int i = threadIdx.x; i < q_width + k_width; i += QKN_THREADS) {
-    float v = le::to_f32(row[i]);
-    if (bias != nullptr) v += bias[i];
-    s_x[i] = v;
-    if (i < q_width) ss_q = fmaf(v, v, ss_q);
-    else ss_k = fmaf(v, v, ss_k);
+  // rows, pages and the rotated halves in 16-byte pieces where the sizes allow it
+  constexpr int PIECE = le::Piece16<T>::COUNT;
+  const bool pieces = head_dim % PIECE == 0 && (rot / 2) % PIECE == 0 && row_stride % PIECE == 0 &&
+                      ((reinterpret_cast<uintptr_t>(rows) | reinterpret_cast<uintptr_t>(k_cache) |
+                        reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0;
+  if (pieces) {
+    for (int i = threadIdx.x * PIECE; i < q_width + k_width; i += QKN_THREADS * PIECE) {
+      float v[PIECE];
+      le::load_piece16<T>(v, row + i);
+#pragma unroll
+      for (int e = 0; e < PIECE; ++e) {
+        if (bias != nullptr) v[e] += bias[i + e];
+        s_x[i + e] = v[e];
+        if (i < q_width) ss_q = fmaf(v[e], v[e], ss_q);
+        else ss_k = fmaf(v[e], v[e], ss_k);
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < q_width + k_width; i += QKN_THREADS) {
+      float v = le::to_f32(row[i]);
+      if (bias != nullptr) v += bias[i];
+      s_x[i] = v;
+      if (i < q_width) ss_q = fmaf(v, v, ss_q);
+      else ss_k = fmaf(v, v, ss_k);
+    }
   }
   if (w_q != nullptr) {
-    ss_q = le::block_sum(ss_q, scratch);
-    ss_k = le::block_sum(ss_k, scratch);
+    // both sums of squares in one meeting of the block
+    ss_q = le::warp_sum(ss_q);
+    ss_k = le::warp_sum(ss_k);
+    if ((threadIdx.x & 31) == 0) scratch2[threadIdx.x >> 5] = make_float2(ss_q, ss_k);
+    __syncthreads();
+    ss_q = ss_k = 0.0f;
+#pragma unroll
+    for (int wi = 0; wi < QKN_THREADS / 32; ++wi) ss_q += scratch2[wi].x, ss_k += scratch2[wi].y;
     const float inv_q = rsqrtf(ss_q / static_cast<float>(q_count) + eps);
     const float inv_k = rsqrtf(ss_k / static_cast<float>(k_count) + eps);
     for (int i = threadIdx.x; i < q_width + k_width; i += QKN_THREADS)
@@ -80,6 +108,35 @@ rope_qknorm_store_kernel(T *__restrict__ rows, int64_t row_stride, const float *
   __syncthreads();
   const int half = rot / 2;
   const int64_t page_at = page >= 0 ? (static_cast<int64_t>(page) * kv_heads * page_size + pos % page_size) * head_dim : 0;
+  if (pieces) {
+    for (int i = threadIdx.x * PIECE; i < q_width + k_width; i += QKN_THREADS * PIECE) {
+      const int h = i / head_dim, d = i - h * head_dim;       // (a piece lies within one head and on one side of the halves)
+      uint4 raw;
+      T *e = reinterpret_cast<T *>(&raw);
+#pragma unroll
+      for (int u = 0; u < PIECE; ++u) {
+        float v = s_x[i + u];
+        if (d < half) v = v * s_cos[d + u] - s_x[i + u + half] * s_sin[d + u];
+        else if (d < rot) v = v * s_cos[d + u - half] + s_x[i + u - half] * s_sin[d + u - half];
+        e[u] = le::from_f32<T>(v);
+      }
+      if (i < q_width) *reinterpret_cast<uint4 *>(row + i) = raw;
+      else if (page >= 0) *reinterpret_cast<uint4 *>(k_cache + page_at + static_cast<int64_t>(h - heads) * page_size * head_dim + d) = raw;
+    }
+    if (page >= 0) {
+      for (int i = threadIdx.x * PIECE; i < k_width; i += QKN_THREADS * PIECE) {
+        const int kvh = i / head_dim, d = i - kvh * head_dim;
+        float v[PIECE];
+        le::load_piece16<T>(v, row + q_width + k_width + i);
+        uint4 raw;
+        T *e = reinterpret_cast<T *>(&raw);
+#pragma unroll
+        for (int u = 0; u < PIECE; ++u) e[u] = le::from_f32<T>(bias != nullptr ? v[u] + bias[q_width + k_width + i + u] : v[u]);
+        *reinterpret_cast<uint4 *>(v_cache + page_at + static_cast<int64_t>(kvh) * page_size * head_dim + d) = raw;
+      }
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < q_width + k_width; i += QKN_THREADS) {
     const int h = i / head_dim, d = i - h * head_dim;
     float v = s_x[i];

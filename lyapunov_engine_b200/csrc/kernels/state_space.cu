@@ -27,8 +27,10 @@
 
 namespace {
 
-constexpr int SSM_THREADS = 128;
+constexpr int SSM_THREADS = 256;
 constexpr int SSM_TILE = 16;
+constexpr int SSM_GROUP = 1;      // tokens whose instructions overlap (SSM_TILE is a multiple); more than 1 did not pay
+constexpr int SSM_AHEAD = 8;      // loads a staging thread has in flight
 
 __device__ __forceinline__ float softplus_f32(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
 
@@ -101,45 +103,115 @@ ssm_scan_kernel(SsmArgs p) {
   for (int t0 = 0; t0 < q_len; t0 += SSM_TILE) {
     const int tile = min(SSM_TILE, q_len - t0);
     __syncthreads();                                   // the tile before is stored
-    for (int i = threadIdx.x; i < tile * N; i += threads) {
-      const int t = i / N, n = i - t * N;
-      const T *src = bcs + static_cast<int64_t>(first + t0 + t) * p.bc_stride + group * N + n;
-      s_b[t * N + n] = le::to_f32(src[p.b_col]);
-      s_c[t * N + n] = le::to_f32(src[p.c_col]);
-    }
-    for (int i = threadIdx.x; i < tile * ROWS; i += threads) {
-      const int t = i / ROWS, rr = i - t * ROWS;
-      const int64_t tok = first + t0 + t;
-      const int rw = row0 + rr;
-      float xv = 0.0f, dv = 0.0f;
-      if (rw < p.rows) {
-        xv = le::to_f32(xs[tok * p.x_stride + rw]);
-        const int di = PER_ROW ? rw : rw / p.rows_per_head;
-        dv = softplus_f32(le::to_f32(dts[tok * p.dt_stride + di]) + p.dt_bias[di]);
+    const int padded = (tile + SSM_GROUP - 1) / SSM_GROUP * SSM_GROUP;       // whole groups: zeros behind the tile's tokens
+    // B and C of the tile's tokens (every block of a group stages the same ones, so this must be cheap): in 16-byte
+    // pieces where the layout allows, else value by value with SSM_AHEAD loads in flight per thread (a load and its
+    // store one after the other would wait out the memory's latency once per value)
+    constexpr int PIECE = le::Piece16<T>::COUNT;
+    const bool pieces = N % PIECE == 0 && p.b_col % PIECE == 0 && p.c_col % PIECE == 0 && p.bc_stride % PIECE == 0 &&
+                        (reinterpret_cast<uintptr_t>(bcs) & 15) == 0;
+    if (pieces) {
+      const int per_token = N / PIECE;
+      for (int i = threadIdx.x; i < padded * per_token; i += threads) {
+        const int t = i / per_token, n = (i - t * per_token) * PIECE;
+        float bv[PIECE], cv[PIECE];
+        if (t < tile) {
+          const T *src = bcs + static_cast<int64_t>(first + t0 + t) * p.bc_stride + group * N + n;
+          le::load_piece16<T>(bv, src + p.b_col);
+          le::load_piece16<T>(cv, src + p.c_col);
+        } else {
+#pragma unroll
+          for (int v = 0; v < PIECE; ++v) bv[v] = cv[v] = 0.0f;
+        }
+#pragma unroll
+        for (int v = 0; v < PIECE; v += 4) {
+          *reinterpret_cast<float4 *>(s_b + t * N + n + v) = make_float4(bv[v], bv[v + 1], bv[v + 2], bv[v + 3]);
+          *reinterpret_cast<float4 *>(s_c + t * N + n + v) = make_float4(cv[v], cv[v + 1], cv[v + 2], cv[v + 3]);
+        }
       }
-      s_x[t * ROWS + rr] = xv;
-      s_dt[t * ROWS + rr] = dv;
+    } else {
+      for (int base = threadIdx.x; base < padded * N; base += threads * SSM_AHEAD) {
+        float bv[SSM_AHEAD], cv[SSM_AHEAD];
+#pragma unroll
+        for (int u = 0; u < SSM_AHEAD; ++u) {
+          const int i = base + u * threads;
+          const int t = i / N, n = i - t * N;
+          bv[u] = cv[u] = 0.0f;
+          if (i < padded * N && t < tile) {
+            const T *src = bcs + static_cast<int64_t>(first + t0 + t) * p.bc_stride + group * N + n;
+            bv[u] = le::to_f32(src[p.b_col]), cv[u] = le::to_f32(src[p.c_col]);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < SSM_AHEAD; ++u) {
+          const int i = base + u * threads;
+          if (i < padded * N) s_b[i] = bv[u], s_c[i] = cv[u];
+        }
+      }
+    }
+    for (int base = threadIdx.x; base < padded * ROWS; base += threads * SSM_AHEAD) {
+      float xs_[SSM_AHEAD], ds_[SSM_AHEAD];
+      int di_[SSM_AHEAD];
+#pragma unroll
+      for (int u = 0; u < SSM_AHEAD; ++u) {
+        const int i = base + u * threads;
+        const int t = i / ROWS, rr = i - t * ROWS;
+        const int rw = row0 + rr;
+        xs_[u] = 0.0f, ds_[u] = -INFINITY, di_[u] = -1;
+        if (i < padded * ROWS && rw < p.rows && t < tile) {
+          const int64_t tok = first + t0 + t;
+          xs_[u] = le::to_f32(xs[tok * p.x_stride + rw]);
+          di_[u] = PER_ROW ? rw : rw / p.rows_per_head;
+          ds_[u] = le::to_f32(dts[tok * p.dt_stride + di_[u]]);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < SSM_AHEAD; ++u) {
+        const int i = base + u * threads;
+        if (i < padded * ROWS) {
+          s_x[i] = xs_[u];
+          s_dt[i] = di_[u] >= 0 ? softplus_f32(ds_[u] + p.dt_bias[di_[u]]) : 0.0f;
+        }
+      }
     }
     __syncthreads();
     if (active && has_state) {
-      for (int t = 0; t < tile; ++t) {
-        const float dv = s_dt[t * ROWS + r], xv = s_x[t * ROWS + r];
-        const float dx = dv * xv;
-        float acc = 0.0f;
-        float decay_all = 0.0f;
-        if constexpr (!PER_ROW) decay_all = le::exp_unbiased(dv * a[0]);
+      // Tokens in groups of SSM_GROUP: the state's chain runs through them one after the other, but each token's
+      // decays, products and the reduction of its sum over the lanes depend on nothing of the others, so the
+      // instructions of a group overlap (a token by itself waits out the latencies of its shuffles and exponentials).
+      // A tile's rows beyond its tokens hold zeros: a step size of zero leaves the state as it is.
+      for (int t = 0; t < tile; t += SSM_GROUP) {
+        float dv[SSM_GROUP], dx[SSM_GROUP], xv[SSM_GROUP], acc[SSM_GROUP], decay_all[SSM_GROUP];
+#pragma unroll
+        for (int u = 0; u < SSM_GROUP; ++u) {
+          dv[u] = s_dt[(t + u) * ROWS + r], xv[u] = s_x[(t + u) * ROWS + r];
+          dx[u] = dv[u] * xv[u];
+          acc[u] = 0.0f;
+          decay_all[u] = PER_ROW ? 0.0f : le::exp_unbiased(dv[u] * a[0]);
+        }
 #pragma unroll
         for (int j = 0; j < NPER; ++j) {
           const int n = lane + LANES * j;
           if (n < N) {
-            const float decay = PER_ROW ? le::exp_unbiased(dv * a[j]) : decay_all;
-            S[j] = fmaf(decay, S[j], dx * s_b[t * N + n]);
-            acc = fmaf(S[j], s_c[t * N + n], acc);
+            float decay[SSM_GROUP];
+#pragma unroll
+            for (int u = 0; u < SSM_GROUP; ++u) decay[u] = PER_ROW ? le::exp_unbiased(dv[u] * a[j]) : decay_all[u];
+#pragma unroll
+            for (int u = 0; u < SSM_GROUP; ++u) {
+              S[j] = fmaf(decay[u], S[j], dx[u] * s_b[(t + u) * N + n]);
+              acc[u] = fmaf(S[j], s_c[(t + u) * N + n], acc[u]);
+            }
           }
         }
 #pragma unroll
-        for (int o = LANES / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        if (lane == 0) s_y[t * ROWS + r] = fmaf(d_skip, xv, acc);
+        for (int o = LANES / 2; o > 0; o >>= 1) {
+#pragma unroll
+          for (int u = 0; u < SSM_GROUP; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], o);
+        }
+        if (lane == 0) {
+#pragma unroll
+          for (int u = 0; u < SSM_GROUP; ++u) s_y[(t + u) * ROWS + r] = fmaf(d_skip, xv[u], acc[u]);
+        }
       }
     }
     __syncthreads();
@@ -194,32 +266,42 @@ int launch_ssm_lanes(const SsmArgs &p, int per_row, int num_requests, cudaStream
 
 }  // namespace
 
-// How many threads share a row's state of `n_state` numbers.
-LE_API int le_ssm_scan_lanes(int n_state) {
+// How many threads share a row's state of `n_state` numbers.  One decay per head: up to 8 entries a thread (the
+// block's rows share staged B and C, and many rows a block amortise that staging).  A decay per row and state: an
+// exponential per entry is the work, and a request's rows times these lanes are all the threads a prompt has, so
+// one or two entries a thread (`spread`; not in a step of single tokens, which only moves the states through).
+static int ssm_lanes(int n_state, int spread) {
   int lanes = 4;
-  while (lanes < 32 && (n_state + lanes - 1) / lanes > 8) lanes *= 2;
+  while (lanes < 32 && (n_state + lanes - 1) / lanes > (spread ? 1 : 8)) lanes *= 2;
   return lanes;
 }
 
-// The rows a block takes: the most that fit its threads and divide a group's rows (a block's rows share B and C).
-LE_API int le_ssm_scan_rows_per_block(int n_state, int rows_per_group) {
-  const int most = SSM_THREADS / le_ssm_scan_lanes(n_state);
-  int rows = 1;
-  for (int c = 1; c <= most; ++c)
-    if (rows_per_group % c == 0) rows = c;
-  return rows;
+// The rows a block takes: a divisor of a group's rows (a block's rows share B and C) that fits its threads.  One
+// decay per head: the most that fit.  A decay per row and state: the most that still leave two blocks for every
+// multiprocessor (a block of a warp at least).
+static int ssm_rows_per_block(int n_state, int rows, int rows_per_group, int spread, int num_requests) {
+  const int lanes = ssm_lanes(n_state, spread);
+  const int most = SSM_THREADS / lanes;
+  int best = 1, roomy = 0;
+  for (int c = 1; c <= most; ++c) {
+    if (rows_per_group % c) continue;
+    best = c;
+    if (static_cast<int64_t>(rows / c) * num_requests >= 296 || c * lanes <= 32) roomy = c;
+  }
+  return spread && roomy > 0 ? roomy : best;
 }
 
 // x [T, rows] (row stride x_stride), bc: rows holding B [groups, n_state] at column b_col and C at c_col, dt
 // [T, rows or heads], z [T, rows] or null: all of type `dtype`; out [T, rows] of type `out_dtype`.  per_row 1: dt,
 // dt_bias and d_skip have one entry per row and a_log is [rows, n_state]; 0: one per head of rows_per_head rows.
-// state: float32 [num_state_rows, rows, n_state]; request b (tokens cu_q[b] .. cu_q[b + 1]) owns row state_slots[b].
+// state: float32 [num_state_rows, rows, n_state]; request b (tokens cu_q[b] .. cu_q[b + 1]) owns row state_slots[b];
+// num_tokens: the step's tokens in all (it only chooses the launch's shape).
 LE_API int le_ssm_scan(void *out, int out_dtype, int64_t out_stride, const void *x, int64_t x_stride, const void *bc,
                        int64_t bc_stride, int b_col, int c_col, const void *dt, int64_t dt_stride, const void *z,
                        int64_t z_stride, int dtype, const float *dt_bias, const float *a_log, const float *d_skip,
                        float *state, int num_state_rows, const int32_t *state_slots, const int32_t *cu_q, int num_requests,
-                       int rows, int n_state, int rows_per_head, int rows_per_group, int per_row, float out_scale,
-                       cudaStream_t stream) {
+                       int num_tokens, int rows, int n_state, int rows_per_head, int rows_per_group, int per_row,
+                       float out_scale, cudaStream_t stream) {
   if (num_requests <= 0 || rows <= 0) return 0;
   if (num_requests > 65535) return le::invalid("le_ssm_scan: too many requests for one launch");
   if (n_state < 1 || rows_per_head < 1 || rows_per_group < 1 || rows % rows_per_group || rows_per_group % rows_per_head)
@@ -230,8 +312,9 @@ LE_API int le_ssm_scan(void *out, int out_dtype, int64_t out_stride, const void 
   p.dt_bias = dt_bias, p.a_log = a_log, p.d_skip = d_skip, p.state = state, p.num_state_rows = num_state_rows;
   p.state_slots = state_slots, p.cu_q = cu_q, p.rows = rows, p.n_state = n_state, p.rows_per_head = rows_per_head;
   p.rows_per_group = rows_per_group, p.out_scale = out_scale;
-  p.rows_per_block = le_ssm_scan_rows_per_block(n_state, rows_per_group);
-  const int lanes = le_ssm_scan_lanes(n_state);
+  const int spread = per_row && num_tokens > num_requests;
+  p.rows_per_block = ssm_rows_per_block(n_state, rows, rows_per_group, spread, num_requests);
+  const int lanes = ssm_lanes(n_state, spread);
 #define LE_SSM(T, TO)                                                                              \
   do {                                                                                             \
     if (lanes == 4) return launch_ssm_lanes<T, TO, 4>(p, per_row, num_requests, stream);           \

@@ -104,10 +104,8 @@ _CORE_SIGNATURES = {
                      c_void_p],
     "le_stream_entry": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "le_sigmoid_gate": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_float, c_void_p],
-    "le_ssm_scan_lanes": [c_int],
-    "le_ssm_scan_rows_per_block": [c_int, c_int],
     "le_ssm_scan": [c_void_p, c_int, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p,
-                    c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                    c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                     c_int, c_int, c_int, c_float, c_void_p],
     "le_mlstm_rows": [c_int, c_int],
     "le_mlstm_scan": [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
@@ -1468,7 +1466,7 @@ def ssm_scan(out, x, bc, b_col: int, c_col: int, dt, z, dt_bias, a_log, d_skip, 
     _check(core().le_ssm_scan(_ptr(out), dtype_code(out.dtype), out.stride(0), _ptr(x), x.stride(0), _ptr(bc), bc.stride(0),
                               int(b_col), int(c_col), _ptr(dt), dt.stride(0), _ptr(z), z.stride(0) if z is not None else 0,
                               dtype_code(x.dtype), _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(state), state.shape[0],
-                              _ptr(state_slots), _ptr(cu_q), int(num_requests), rows, int(n_state), int(rows_per_head),
+                              _ptr(state_slots), _ptr(cu_q), int(num_requests), T, rows, int(n_state), int(rows_per_head),
                               int(rows_per_group), 1 if per_row else 0, float(out_scale), _stream()), "le_ssm_scan")
 
 
