@@ -14,7 +14,8 @@
     "mlp": {"kind": "moe", "expert": {"ff"}, "router": {"experts", "top"}, "shared": {"ff"}} | null
 
 Every size and constant a layer uses is read from its own entry; nothing has a
-default.  Keys that may be absent, and what their absence means: ``mlp`` null
+default.  Keys that may be absent, and what their absence means: ``embedding``
+(the embedding is not scaled), ``mlp`` null
 (a layer without feed-forward), ``shared`` (no shared expert), an attention's
 ``mask`` (every earlier key is visible; ``keep_first`` absent: the window
 keeps no first keys), ``softcap`` (scores are not capped), ``rot.scaling``
@@ -114,7 +115,8 @@ class RibozenConfig:
         r = KeyReader(raw, source)
         width = r.integer("width")
         norm = KeyReader(r.mapping("norm"), source + ": norm")
-        embedding = KeyReader(r.mapping("embedding"), source + ": embedding")
+        raw_embedding = r.mapping("embedding", None)
+        embedding = KeyReader(raw_embedding, source + ": embedding") if raw_embedding is not None else None
         entries = raw.get("layers")
         if not isinstance(entries, list) or not entries:
             raise ConfigError(f"{source}: 'layers' must be a non-empty list")
@@ -162,7 +164,8 @@ class RibozenConfig:
                                       f"{feed_forward.experts} experts")
             layers.append(RibozenLayer(kind, mixer, feed_forward))
         return RibozenConfig(architecture=r.string("architecture"), vocab=r.integer("vocab"), width=width,
-                             norm_eps=norm.number("eps"), embedding_scale=embedding.number("scale", positive=False),
+                             norm_eps=norm.number("eps"),
+                             embedding_scale=embedding.number("scale", positive=False) if embedding is not None else 1.0,
                              layers=tuple(layers), raw=dict(raw))
 
 

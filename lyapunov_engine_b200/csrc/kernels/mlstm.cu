@@ -242,7 +242,15 @@ template <typename T, int NPER, int LANES>
 int launch_mlstm(const MlstmArgs &p, int num_requests, cudaStream_t stream) {
   const dim3 grid(p.vdim / p.rows_per_block, p.heads, num_requests);
   const size_t smem = sizeof(float) * (2 * ML_TILE * p.dim + 2 * ML_TILE * p.rows_per_block + 6 * ML_TILE);
-  if (smem > 48 * 1024) return le::invalid("le_mlstm_scan: heads of %d entries do not fit a block's shared memory", p.dim);
+  if (smem > 200 * 1024) return le::invalid("le_mlstm_scan: heads of %d entries do not fit a block's shared memory", p.dim);
+  if (smem > 48 * 1024) {
+    static size_t raised = 0;                    // per form and process: the most asked for so far
+    if (smem > raised) {
+      cudaError_t e = cudaFuncSetAttribute(mlstm_scan_kernel<T, NPER, LANES>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      if (e != cudaSuccess) return le::invalid("le_mlstm_scan: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+      raised = smem;
+    }
+  }
   return le::launch_chained(mlstm_scan_kernel<T, NPER, LANES>, grid, dim3((p.rows_per_block + 1) * LANES), smem, stream, p);
 }
 

@@ -242,10 +242,18 @@ int launch_ssm(const SsmArgs &p, int per_row, int num_requests, cudaStream_t str
   const int rows_per_block = p.rows_per_block;
   const dim3 grid((p.rows + rows_per_block - 1) / rows_per_block, num_requests);
   const size_t smem = sizeof(float) * (2 * SSM_TILE * p.n_state + 3 * SSM_TILE * rows_per_block);
-  if (smem > 48 * 1024) return le::invalid("le_ssm_scan: %d numbers of state per row do not fit a block's shared memory", p.n_state);
+  if (smem > 200 * 1024) return le::invalid("le_ssm_scan: %d numbers of state per row do not fit a block's shared memory", p.n_state);
   const dim3 block(rows_per_block * LANES);
-  if (per_row) return le::launch_chained(ssm_scan_kernel<T, TO, NPER, LANES, true>, grid, block, smem, stream, p);
-  return le::launch_chained(ssm_scan_kernel<T, TO, NPER, LANES, false>, grid, block, smem, stream, p);
+  auto kernel = per_row ? ssm_scan_kernel<T, TO, NPER, LANES, true> : ssm_scan_kernel<T, TO, NPER, LANES, false>;
+  if (smem > 48 * 1024) {
+    static size_t raised[2] = {0, 0};            // per form and process: the most asked for so far
+    if (smem > raised[per_row ? 1 : 0]) {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      if (e != cudaSuccess) return le::invalid("le_ssm_scan: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+      raised[per_row ? 1 : 0] = smem;
+    }
+  }
+  return le::launch_chained(kernel, grid, block, smem, stream, p);
 }
 
 template <typename T, typename TO, int LANES>

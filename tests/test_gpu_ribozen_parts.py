@@ -87,6 +87,7 @@ SCANS = [
     (1, 20, 5, 1, True, (33, 6), ((1, 32), (2, 2, 2))),
     (1, 64, 16, 1, True, (70, 18, 5), ((64, 2, 4), (18,), (1, 4))),
     (2, 24, 130, 1, False, (19,), ((3, 16),)),
+    (1, 8, 512, 1, False, (18,), ((2, 16),)),                       # more shared memory than a block has by default
 ]
 
 
@@ -175,6 +176,7 @@ MEMORIES = [
     (1, 64, 64, 12.0, (40, 21), ((17, 23), (1, 20))),
     (3, 5, 3, 2.0, (33, 6, 18), ((1, 32), (2, 2, 2), (18,))),
     (2, 130, 8, 15.0, (19,), ((3, 16),)),
+    (1, 512, 4, 9.0, (18,), ((2, 16),)),                            # more shared memory than a block has by default
 ]
 
 

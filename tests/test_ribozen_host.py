@@ -51,7 +51,7 @@ def test_config_is_read_key_by_key():
     left = c.layers[1].mixer.left
     assert (left.window, left.keep_first, left.softcap, left.rot_scaling.factor) == (6, 2, 20.0, 4.0)
     assert c.layers[1].feed_forward is None and c.layers[2].feed_forward.shared_ff == 0 and c.layers[0].feed_forward.shared_ff == 16
-    required = [("vocab",), ("width",), ("norm",), ("embedding",), ("embedding", "scale"), ("layers", 0, "mixer", "heads"),
+    required = [("vocab",), ("width",), ("norm",), ("embedding", "scale"), ("layers", 0, "mixer", "heads"),
                 ("layers", 0, "mixer", "state"), ("layers", 0, "mixer", "groups"), ("layers", 0, "mixer", "conv"),
                 ("layers", 0, "mixer", "norm_groups"), ("layers", 0, "mlp", "expert"), ("layers", 0, "mlp", "router", "top"),
                 ("layers", 1, "mixer", "left_scale"), ("layers", 1, "mixer", "right"), ("layers", 1, "mixer", "left", "scale"),
@@ -73,8 +73,10 @@ def test_config_is_read_key_by_key():
 def test_keys_that_may_be_absent():
     for path in (("layers", 1, "mixer", "left", "mask"), ("layers", 1, "mixer", "left", "mask", "keep_first"),
                  ("layers", 1, "mixer", "left", "softcap"), ("layers", 1, "mixer", "left", "rot", "scaling"),
-                 ("layers", 0, "mlp", "shared")):
+                 ("layers", 0, "mlp", "shared"), ("embedding",)):
         c = RibozenConfig.from_dict(edit(CFG, path, delete=True))
+        if path[-1] == "embedding":
+            assert c.embedding_scale == 1.0
         left = c.layers[1].mixer.left
         if path[-1] == "mask":
             assert (left.window, left.keep_first) == (0, 0)
