@@ -1608,7 +1608,7 @@ def run_zepilix(args):
 
 # ---------------------------------------------------------------------------------------------- Ribozen
 RIBOZEN_WINDOW = 1024       # keys an attention layer's query sees at most, beside the first RIBOZEN_KEPT
-RIBOZEN_KEPT = 4
+RIBOZEN_KEPT = 8
 RIBOZEN_STATE = 128         # numbers of state per channel of a state-space-duality layer
 RIBOZEN_SCAN_STATE = 16     # of a selective-scan channel
 RIBOZEN_EXPERTS, RIBOZEN_TOP = 8, 2
@@ -1626,10 +1626,10 @@ def ribozen_config(llama: dict) -> dict:
                "mixer": {"heads": 2 * W // 64, "vdim": 64, "state": RIBOZEN_STATE, "groups": 8, "conv": 4, "norm_groups": 8}}
     memory = {"type": "mlstm", "mlp": mlp, "mixer": {"heads": W // 256, "dim": 128, "vdim": 256, "gate_cap": 15.0}}
     pair = {"type": "parallel", "mlp": mlp,
-            "mixer": {"left_scale": 0.6, "right_scale": 1.1,
-                      "left": {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "softcap": 50.0,
+            "mixer": {"left_scale": 0.7, "right_scale": 1.0,
+                      "left": {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "softcap": 30.0,
                                "rot": {"dims": hd, "base": 500000.0,
-                                       "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}},
+                                       "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}},
                                "mask": {"size": RIBOZEN_WINDOW, "keep_first": RIBOZEN_KEPT}},
                       "right": {"inner": W, "state": RIBOZEN_SCAN_STATE, "dt_rank": W // 16, "conv": 4}}}
     kinds = (duality, duality, memory, pair)
@@ -1757,7 +1757,7 @@ def ribozen_kernel_rows(pk, llama):
         row(f"state-space recurrence, {Cs} channels x {Ns} (a decay per channel and state), {reqs} request(s)",
             "delta rule, 16 heads of 128 x 128", T, reqs * 2 * 4 * Cs * Ns + 4 * Cs * Ns + T * (Cs * 8 + Ns * 4),
             lambda i: ops.ssm_scan(outs, convs, low, R, R + Ns, dt, z, zeros_c, a_log, zeros_c, states[i], slots, cu, reqs, Ns, 1, Cs,
-                                   per_row=True, out_scale=1.1), state_sets, fp32_flops=6 * T * Cs * Ns)
+                                   per_row=True, out_scale=1.0), state_sets, fp32_flops=6 * T * Cs * Ns)
         del states
         # matrix memory
         Hm, d, e = mm["heads"], mm["dim"], mm["vdim"]
@@ -1798,7 +1798,7 @@ def ribozen_kernel_rows(pk, llama):
         qkv = torch.randn(T, (2 * nh + 2 * nkv) * hd, device=dev).to(bf)
         kc = torch.zeros(pages + 1, nkv, page, hd, device=dev, dtype=bf)
         vc = torch.zeros_like(kc)
-        rates, magnitude = ramped_rates(hd, 5e5, {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0})
+        rates, magnitude = ramped_rates(hd, 5e5, {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0})
         rates = rates.to(dev)
         bias = torch.zeros((nh + 2 * nkv) * hd, device=dev)
         wq, wk = torch.ones(nh * hd, device=dev), torch.ones(nkv * hd, device=dev)
@@ -1813,7 +1813,7 @@ def ribozen_kernel_rows(pk, llama):
         attn = torch.randn(T, nh * hd, device=dev).to(bf)
         side = torch.empty(T, nh * hd + W, device=dev, dtype=bf)
         row("gate per entry (sigmoid) into the shared buffer", "norm per head times silu gate", T, T * nh * hd * 6,
-            lambda i: ops.sigmoid_gate(side[:, :nh * hd], attn, qkv[:, (nh + 2 * nkv) * hd:], 0.6), 1)
+            lambda i: ops.sigmoid_gate(side[:, :nh * hd], attn, qkv[:, (nh + 2 * nkv) * hd:], 0.7), 1)
         # the layer scale in the norm's kernel
         resid = [torch.randn(T, W, device=dev) for _ in range(8)]
         delta = torch.randn(T, W, device=dev).to(bf)
@@ -1839,7 +1839,7 @@ def ribozen_kernel_rows(pk, llama):
         seen = sum(min(t, RIBOZEN_WINDOW + RIBOZEN_KEPT) for t in total) if T == B else \
             sum(min(p + 1, RIBOZEN_WINDOW + RIBOZEN_KEPT) for p in range(2048)) // 128       # keys a 128-row tile reads, roughly
         nbytes = (seen if T == B else 2048 * 16 // 128 * 0 + 16 * (RIBOZEN_WINDOW + 128)) * nkv * hd * 4 + T * nh * hd * 4
-        for name, keep, cap in (("kept first keys + capped scores", RIBOZEN_KEPT, 50.0), ("window alone", 0, 0.0)):
+        for name, keep, cap in (("kept first keys + capped scores", RIBOZEN_KEPT, 30.0), ("window alone", 0, 0.0)):
             if T == B:
                 splits = 4
                 scratch = torch.zeros(max(ops.attention_decode_scratch_floats(hd, B, nh, splits), 1), device=dev)

@@ -87,7 +87,7 @@ CONFIGS = {
     "c": ({"architecture": "Ribozen", "vocab": 300, "width": 128, "norm": {"eps": 1e-5}, "embedding": {"scale": 11.3},
            "layers": [parallel(left(4, 2, 64, 64, 0.25, 64, 1e4), right(128, 16, 8, 4), 0.5, 0.5, moe(128, 8, 2, 0)),
                       mamba2(4, 32, 64, 2, 4, 2, None),
-                      parallel(left(4, 1, 64, 32, 0.3, 32, 5e5, window=70, keep_first=5, softcap=30.0, scaling=(4.0, 128, 32.0, 1.0)),
+                      parallel(left(6, 2, 64, 32, 0.3, 32, 5e5, window=70, keep_first=5, softcap=30.0, scaling=(6.0, 128, 16.0, 2.0)),
                                right(256, 16, 16, 4), 0.6, 1.1, moe(64, 4, 1, 64)),
                       mlstm(2, 64, 64, 12.0, None),
                       parallel(left(2, 2, 128, 128, 0.15, 64, 1e6, window=33, keep_first=1), right(64, 8, 4, 3), 1.3, 0.4, None)]}, 16),

@@ -234,7 +234,7 @@ ENCODINGS = [
     # heads, kv heads, dim, vdim, padded, rot, base, scaling, page
     (4, 2, 16, 24, 32, 8, 1e4, {"factor": 8.0, "original": 64, "fast": 16.0, "slow": 2.0}, 8),
     (3, 1, 24, 10, 32, 10, 1e3, None, 4),
-    (2, 2, 64, 64, 64, 64, 5e5, {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}, 16),
+    (2, 2, 64, 64, 64, 64, 5e5, {"factor": 6.0, "original": 1024, "fast": 16.0, "slow": 2.0}, 16),
     (1, 1, 16, 16, 16, 0, 1e4, None, 16),
 ]
 
@@ -349,7 +349,7 @@ def build_attention(dtype, nh, nkv, hd, page, q_lens, ctx_before, seed, window, 
 KEPT = [
     # nh, nkv, hd, page, q_lens, ctx_before, window, keep, cap, scale
     (4, 2, 16, 4, [5, 1, 17, 1], [0, 9, 30, 3], 8, 3, 6.0, 0.4),
-    (4, 1, 64, 16, [200, 1, 1, 130, 1], [0, 136, 139, 150, 700], 136, 4, 50.0, 0.125),       # sizes the tensor cores take whole
+    (4, 2, 64, 16, [200, 1, 1, 130, 1], [0, 120, 123, 150, 700], 120, 5, 40.0, 0.11),       # sizes the tensor cores take whole
     (2, 2, 32, 8, [33, 1, 1, 2], [100, 69, 70, 300], 20, 70, 0.0, 0.3),                        # more kept keys than the window holds, in two tiles
     (6, 3, 48, 16, [1, 1, 1, 1], [15, 16, 17, 400], 16, 1, 3.0, 0.2),
     (2, 1, 128, 32, [140, 1], [120, 513], 65, 33, 30.0, 0.09),

@@ -21,10 +21,10 @@ CFG = {"architecture": "Ribozen", "vocab": 50, "width": 32, "norm": {"eps": 1e-5
        "layers": [{"type": "mamba2", "mixer": {"heads": 4, "vdim": 8, "state": 6, "groups": 2, "conv": 3, "norm_groups": 2},
                    "mlp": MOE},
                   {"type": "parallel",
-                   "mixer": {"left_scale": 0.6, "right_scale": 1.1,
+                   "mixer": {"left_scale": 0.8, "right_scale": 1.3,
                              "left": {"heads": 4, "kv_heads": 2, "dim": 8, "vdim": 12, "scale": 0.3, "softcap": 20.0,
                                       "rot": {"dims": 4, "base": 100.0,
-                                              "scaling": {"factor": 4.0, "original": 32, "fast": 8.0, "slow": 1.0}},
+                                              "scaling": {"factor": 3.0, "original": 32, "fast": 8.0, "slow": 1.0}},
                                       "mask": {"size": 6, "keep_first": 2}},
                              "right": {"inner": 24, "state": 5, "dt_rank": 3, "conv": 2}},
                    "mlp": None},
@@ -49,7 +49,7 @@ def test_config_is_read_key_by_key():
     assert (c.vocab, c.width, c.norm_eps, c.embedding_scale) == (50, 32, 1e-5, 3.0)
     assert [layer.kind for layer in c.layers] == ["mamba2", "parallel", "mlstm"]
     left = c.layers[1].mixer.left
-    assert (left.window, left.keep_first, left.softcap, left.rot_scaling.factor) == (6, 2, 20.0, 4.0)
+    assert (left.window, left.keep_first, left.softcap, left.rot_scaling.factor) == (6, 2, 20.0, 3.0)
     assert c.layers[1].feed_forward is None and c.layers[2].feed_forward.shared_ff == 0 and c.layers[0].feed_forward.shared_ff == 16
     required = [("vocab",), ("width",), ("norm",), ("embedding", "scale"), ("layers", 0, "mixer", "heads"),
                 ("layers", 0, "mixer", "state"), ("layers", 0, "mixer", "groups"), ("layers", 0, "mixer", "conv"),
@@ -124,7 +124,7 @@ def test_pages_of_kept_first_keys_are_never_given_back():
 
 
 def test_ramped_rates():
-    for dims, base, scaling in ((8, 1e4, None), (64, 5e4, {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}),
+    for dims, base, scaling in ((8, 1e4, None), (64, 5e4, {"factor": 6.0, "original": 1024, "fast": 16.0, "slow": 2.0}),
                                 (6, 50.0, {"factor": 8.0, "original": 16, "fast": 4.0, "slow": 0.25})):
         rates, magnitude = ramped_rates(dims, base, scaling)
         want, want_magnitude = pr.scaled_rates(dims, base, scaling)
