@@ -15,11 +15,10 @@
 
 Every size and constant a layer uses is read from its own entry; nothing has a
 default.  Keys that may be absent, and what their absence means: ``embedding``
-(the embedding is not scaled), ``mlp`` null
-(a layer without feed-forward), ``shared`` (no shared expert), an attention's
-``mask`` (every earlier key is visible; ``keep_first`` absent: the window
-keeps no first keys), ``softcap`` (scores are not capped), ``rot.scaling``
-(plain rotary rates).
+(the embedding is not scaled), ``mlp`` null (a layer without feed-forward),
+``shared`` (no shared expert), an attention's ``mask`` (every earlier key is
+visible; ``keep_first`` absent: the window keeps no first keys), ``softcap``
+(scores are not capped), ``rot.scaling`` (plain rotary rates).
 """
 from __future__ import annotations
 
