@@ -57,6 +57,7 @@ ssm_scan_kernel(SsmArgs p) {
   float *s_x = s_c + SSM_TILE * N;             // [TILE][ROWS]
   float *s_dt = s_x + SSM_TILE * ROWS;         // [TILE][ROWS]
   float *s_y = s_dt + SSM_TILE * ROWS;         // [TILE][ROWS]
+  float *s_dec = s_y + SSM_TILE * ROWS;        // [TILE][ROWS]: the decay of a row's head (one decay per head only)
   le::let_successor_start();
   const int b = blockIdx.y;
   const int row0 = blockIdx.x * ROWS;
@@ -169,8 +170,11 @@ ssm_scan_kernel(SsmArgs p) {
       for (int u = 0; u < SSM_AHEAD; ++u) {
         const int i = base + u * threads;
         if (i < padded * ROWS) {
+          const float step = di_[u] >= 0 ? softplus_f32(ds_[u] + p.dt_bias[di_[u]]) : 0.0f;
           s_x[i] = xs_[u];
-          s_dt[i] = di_[u] >= 0 ? softplus_f32(ds_[u] + p.dt_bias[di_[u]]) : 0.0f;
+          s_dt[i] = step;
+          // (one decay per head: made once per row and token here, not by every lane of the row)
+          if constexpr (!PER_ROW) s_dec[i] = di_[u] >= 0 ? le::exp_unbiased(-step * expf(p.a_log[di_[u]])) : 1.0f;
         }
       }
     }
@@ -187,8 +191,9 @@ ssm_scan_kernel(SsmArgs p) {
           dv[u] = s_dt[(t + u) * ROWS + r], xv[u] = s_x[(t + u) * ROWS + r];
           dx[u] = dv[u] * xv[u];
           acc[u] = 0.0f;
-          decay_all[u] = PER_ROW ? 0.0f : le::exp_unbiased(dv[u] * a[0]);
+          decay_all[u] = PER_ROW ? 0.0f : s_dec[(t + u) * ROWS + r];
         }
+        const float *b_at = s_b + t * N + lane, *c_at = s_c + t * N + lane;     // (entry j lies LANES * j further: a constant)
 #pragma unroll
         for (int j = 0; j < NPER; ++j) {
           const int n = lane + LANES * j;
@@ -198,8 +203,8 @@ ssm_scan_kernel(SsmArgs p) {
             for (int u = 0; u < SSM_GROUP; ++u) decay[u] = PER_ROW ? le::exp_unbiased(dv[u] * a[j]) : decay_all[u];
 #pragma unroll
             for (int u = 0; u < SSM_GROUP; ++u) {
-              S[j] = fmaf(decay[u], S[j], dx[u] * s_b[(t + u) * N + n]);
-              acc[u] = fmaf(S[j], s_c[(t + u) * N + n], acc[u]);
+              S[j] = fmaf(decay[u], S[j], dx[u] * b_at[u * N + LANES * j]);
+              acc[u] = fmaf(S[j], c_at[u * N + LANES * j], acc[u]);
             }
           }
         }
@@ -241,7 +246,7 @@ template <typename T, typename TO, int NPER, int LANES>
 int launch_ssm(const SsmArgs &p, int per_row, int num_requests, cudaStream_t stream) {
   const int rows_per_block = p.rows_per_block;
   const dim3 grid((p.rows + rows_per_block - 1) / rows_per_block, num_requests);
-  const size_t smem = sizeof(float) * (2 * SSM_TILE * p.n_state + 3 * SSM_TILE * rows_per_block);
+  const size_t smem = sizeof(float) * (2 * SSM_TILE * p.n_state + 4 * SSM_TILE * rows_per_block);
   if (smem > 200 * 1024) return le::invalid("le_ssm_scan: %d numbers of state per row do not fit a block's shared memory", p.n_state);
   const dim3 block(rows_per_block * LANES);
   auto kernel = per_row ? ssm_scan_kernel<T, TO, NPER, LANES, true> : ssm_scan_kernel<T, TO, NPER, LANES, false>;
